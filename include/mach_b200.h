@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define MACH_ABI_VERSION 2
+#define MACH_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define MACH_API __attribute__((visibility("default")))
@@ -192,10 +192,20 @@ MACH_API int mach_block_fp8_gemm_ordered_static(const void* a, const void* b, co
  * All ranks must call with the same (m, h, algo) in the same order. algo: 0 = choose,
  * 1 = one-shot, 2 = two-shot with one flag per (rank, CTA), 3 = two-shot with one flag per
  * (rank, phase) published by the grid's last CTA (what 0 chooses above 256 KiB with more than
- * two ranks).
- * partial_bf16 may be NULL after mach_mx_gemm_reduce_scatter. norm_out, residual_out,
+ * two ranks; launched cooperatively, so a grid that cannot be co-resident is held back or
+ * refused by the driver instead of spinning).
+ * partial_bf16 may be NULL after mach_mx_gemm_reduce_scatter of the same [m, h] on this
+ * workspace (anything else is refused with MACH_ERR_INVALID). norm_out, residual_out,
  * codes+scales may be NULL.
- * residual_out may alias residual. hidden % 32 == 0, hidden <= 8192, world <= 8. */
+ * residual_out may alias residual. hidden % 32 == 0, hidden <= 8192, world <= 8.
+ *
+ * Failure behaviour: every device-side wait for a peer is bounded (mach_ar_set_wait_limit_us,
+ * about one second by default). A wait that gives up records 401 (scatter flag) or 402 (gather
+ * flag) in the device status word (mach_device_status), marks the workspace as failed and
+ * writes NaN (BF16) / 0x7F (E4M3) / 0xFF (E8M0) into the outputs of the affected rows; every
+ * later call on a failed workspace returns poisoned outputs at once (status 403) until all
+ * ranks have called mach_ar_reset. Poll mach_device_status at a host synchronisation point
+ * (end of a step) to learn of it. */
 MACH_API size_t mach_ar_buffer_bytes(int world, int64_t tokens_cap, int64_t hidden);
 MACH_API int mach_ar_buffer_alloc(size_t bytes, void** dev_ptr); /* zero-filled */
 MACH_API int mach_ar_buffer_free(void* dev_ptr);
@@ -205,6 +215,13 @@ MACH_API int mach_ar_ipc_close(void* peer_ptr);
 MACH_API int mach_ar_create(int world, int rank, int64_t tokens_cap, int64_t hidden,
                             void* const* buffers, void** workspace);
 MACH_API int mach_ar_destroy(void* workspace);
+/* Upper bound of every device-side wait of calls on this workspace (host state, takes effect
+ * with the next call). */
+MACH_API int mach_ar_set_wait_limit_us(void* workspace, int64_t microseconds);
+/* Clears this rank's epoch, flags and failed mark (synchronises `stream`). Collective by
+ * contract: every rank calls it with no reduce in flight, with a host barrier before and after
+ * (the reference re-creates its FlashInfer workspace instead, src/vllm_mach/mxfp6/ar_norm.py:113-128). */
+MACH_API int mach_ar_reset(void* workspace, void* stream);
 MACH_API int mach_allreduce_residual_rmsnorm_mxfp8(void* workspace, const void* partial_bf16,
                                                    const void* residual_bf16,
                                                    const void* gamma_bf16, float eps,
@@ -212,6 +229,42 @@ MACH_API int mach_allreduce_residual_rmsnorm_mxfp8(void* workspace, const void* 
                                                    void* residual_out_bf16, void* codes,
                                                    void* scales, int64_t m, int64_t h, int algo,
                                                    void* stream);
+
+/* Owner form of the same reduce (row ownership between norms; replaces reduce_owner +
+ * gather_mx8 of native/owner_prefill/owner.cu:64-160 for any world <= 8 and any M): rank r owns
+ * rows [first, first + count) given by mach_ar_owner_rows (contiguous blocks of ceil(M / world)).
+ * Every owner pulls its rows of all ranks' partial sums over NVLink, reduces them in rank
+ * order, adds ITS rows of the residual, normalises and quantises them; then every rank pulls
+ * the other owners' codes and scales. Outputs: codes E4M3 [M, H] + swizzled E8M0 scales for ALL
+ * rows on every rank (what the next block-scaled GEMM consumes); residual_out_rows and
+ * norm_out_rows (may be NULL) BF16 [count, H] for the OWNED rows only; residual_rows is BF16
+ * [count, H], the owned rows of the residual stream. Same arithmetic and rounding points as
+ * mach_allreduce_residual_rmsnorm_mxfp8, hence the same bytes.
+ * partial_bf16 == NULL: the producing GEMM wrote its BF16 [M, H] output (leading dimension H)
+ * to the address mach_ar_partial_ptr returns (inside this rank's communication buffer, fixed
+ * for the life of the workspace), which saves one local copy. Launched cooperatively. */
+MACH_API int mach_ar_owner_rows(int world, int rank, int64_t m, int64_t* first, int64_t* count);
+MACH_API int mach_ar_partial_ptr(void* workspace, void** partial_bf16);
+MACH_API int mach_allreduce_owner_rmsnorm_mxfp8(void* workspace, const void* partial_bf16,
+                                                const void* residual_rows_bf16,
+                                                const void* gamma_bf16, float eps,
+                                                float weight_bias, void* norm_out_rows_bf16,
+                                                void* residual_out_rows_bf16, void* codes,
+                                                void* scales, int64_t m, int64_t h, void* stream);
+
+/* All `world` ranks of a group whose communication buffers live on ONE device, run as a
+ * single cooperative grid (kernels that wait on one another must not be separate launches on
+ * one GPU). workspaces[r] must be rank r of `world`; the per-rank arrays hold what rank r
+ * would pass to mach_allreduce_residual_rmsnorm_mxfp8 (owner_form == 0, `algo` as there) or to
+ * mach_allreduce_owner_rmsnorm_mxfp8 (owner_form != 0). For validating the multi-rank
+ * protocols on a machine with fewer GPUs than ranks; no counterpart in the reference. */
+MACH_API int mach_allreduce_local_ranks(int world, void* const* workspaces,
+                                        const void* const* partials,
+                                        const void* const* residuals, const void* gamma_bf16,
+                                        float eps, float weight_bias, void* const* norm_outs,
+                                        void* const* residual_outs, void* const* codes,
+                                        void* const* scales, int64_t m, int64_t h, int algo,
+                                        int owner_form, void* stream);
 
 /* Row-parallel GEMM whose epilogue is the reduce-scatter: the BF16 partial sums [M, N] never go
  * to a local matrix, every row is stored (NVLink peer store) into the all-reduce buffer of the

@@ -24,17 +24,18 @@ int* device_status_ptr();
 bool pdl_enabled();
 void set_pdl_enabled(bool on);
 
-// cudaLaunchKernelEx with an optional cluster (y-dimension) and the programmatic-serialisation
-// attribute.
+// cudaLaunchKernelEx with an optional cluster (y-dimension), the programmatic-serialisation
+// attribute and the cooperative attribute (the whole grid co-resident, or the launch fails).
 template <typename... KArgs, typename... Args>
-cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                      cudaStream_t stream, dim3 cluster, bool pdl, Args&&... args) {
+cudaError_t launch_ex_attrs(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                            cudaStream_t stream, dim3 cluster, bool pdl, bool cooperative,
+                            Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
+  cudaLaunchAttribute attr[3];
   int n = 0;
   if (cluster.x * cluster.y * cluster.z > 1) {
     attr[n].id = cudaLaunchAttributeClusterDimension;
@@ -48,9 +49,21 @@ cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
     attr[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;
   }
+  if (cooperative) {
+    attr[n].id = cudaLaunchAttributeCooperative;
+    attr[n].val.cooperative = 1;
+    ++n;
+  }
   cfg.attrs = attr;
   cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                      cudaStream_t stream, dim3 cluster, bool pdl, Args&&... args) {
+  return launch_ex_attrs(kernel, grid, block, smem, stream, cluster, pdl, false,
+                         static_cast<Args&&>(args)...);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }

@@ -462,6 +462,7 @@ extern "C" int mach_residual_rmsnorm_rounded_mxfp8(const void* a, const void* re
                                                    float weight_bias, void* norm_out,
                                                    void* residual_out, void* codes, void* scales,
                                                    int64_t m, int64_t h, void* stream) {
+  if (m == 0) return MACH_OK;
   if (!residual) return fail(MACH_ERR_INVALID, "residual_rmsnorm_rounded: residual is required");
   return launch_add_rmsnorm(a, residual, gamma, eps, weight_bias, norm_out, residual_out, codes,
                             scales, m, h, true, (cudaStream_t)stream);

@@ -44,14 +44,20 @@ class MxMlpWeights:
                    for t in (self.w_gate_up, self.s_gate_up, self.w_down, self.s_down))
 
 
-def mlp_forward(x: torch.Tensor, w: MxMlpWeights) -> torch.Tensor:
+def mlp_forward(x: torch.Tensor, w: MxMlpWeights, out: torch.Tensor | None = None) -> torch.Tensor:
     """BF16 [M, H] -> BF16 [M, H] (this rank's partial sum when the MLP is sharded)."""
     if x.shape[0] == 0:
         return x.new_empty((0, w.hidden))
     codes, scales = native.quantize_mxfp8(x)
+    return mlp_forward_quantized(codes, scales, w, out)
+
+
+def mlp_forward_quantized(codes, scales, w: MxMlpWeights, out: torch.Tensor | None = None):
+    """The same from MXFP8 activations (codes [M, H] + swizzled scales), which is what a
+    preceding fused norm + quantise hands over (src/vllm_mach/mxfp6/mxfp8_norm_quant.py:83-130)."""
     h_codes, h_scales = native.mx_gemm_swiglu(codes, scales, w.w_gate_up, w.s_gate_up, w.fmt,
                                               w.layout)
-    return native.mx_gemm(h_codes, h_scales, w.w_down, w.s_down, w.fmt)
+    return native.mx_gemm(h_codes, h_scales, w.w_down, w.s_down, w.fmt, out=out)
 
 
 def mlp_block(x, residual, norm_weight, eps: float, w: MxMlpWeights, group=None):
@@ -76,3 +82,29 @@ def mlp_block(x, residual, norm_weight, eps: float, w: MxMlpWeights, group=None)
     norm, res, _, _ = native.add_rmsnorm_mxfp8(partial, residual, norm_weight, eps,
                                                want_quant=False)
     return norm, res
+
+
+def mlp_block_owner(x, residual_rows, norm_weight, eps: float, w: MxMlpWeights, group=None,
+                    want_norm: bool = True):
+    """MLP + deferred reduce with row ownership between norms (native/owner_prefill/owner.cu:
+    64-160): the residual stream is row-owned (`collective.owner_rows`), the down projection
+    writes its partial sums straight into this rank's communication buffer, every owner reduces,
+    normalises and quantises its rows, and every rank receives the MXFP8 codes + scales of all
+    rows for the next layer's GEMM. `x`: BF16 [M, H], or a (codes, scales) pair from the
+    previous block. Returns (codes [M, H], scales, residual_out_rows, norm_rows | None)."""
+    from . import collective
+    quantized = isinstance(x, tuple)
+    m = (x[0] if quantized else x).shape[0]
+    world = torch.distributed.get_world_size(group) if group is not None else 1
+    if world == 1:
+        partial = mlp_forward_quantized(x[0], x[1], w) if quantized else mlp_forward(x, w)
+        norm, res, codes, scales = native.add_rmsnorm_mxfp8(partial, residual_rows, norm_weight,
+                                                            eps, want_norm=want_norm)
+        return codes, scales, res, norm
+    dev = residual_rows.device
+    target = collective.owner_partial_buffer(group, w.hidden, m, dev) if m else None
+    partial = (mlp_forward_quantized(x[0], x[1], w, out=target) if quantized
+               else mlp_forward(x, w, out=target))
+    return collective.allreduce_owner_add_rmsnorm(None if target is not None else partial,
+                                                  residual_rows, norm_weight, eps, group, m,
+                                                  want_norm=want_norm)

@@ -49,6 +49,16 @@ _SIGNATURES = {
     "mach_ar_ipc_close": (_INT, [_P]),
     "mach_ar_create": (_INT, [_INT, _INT, _I64, _I64, ctypes.POINTER(_P), ctypes.POINTER(_P)]),
     "mach_ar_destroy": (_INT, [_P]),
+    "mach_ar_set_wait_limit_us": (_INT, [_P, _I64]),
+    "mach_ar_reset": (_INT, [_P, _P]),
+    "mach_ar_owner_rows": (_INT, [_INT, _INT, _I64, ctypes.POINTER(_I64), ctypes.POINTER(_I64)]),
+    "mach_ar_partial_ptr": (_INT, [_P, ctypes.POINTER(_P)]),
+    "mach_allreduce_owner_rmsnorm_mxfp8": (_INT, [_P, _P, _P, _P, _F, _F, _P, _P, _P, _P, _I64,
+                                                  _I64, _P]),
+    "mach_allreduce_local_ranks": (_INT, [_INT, ctypes.POINTER(_P), ctypes.POINTER(_P),
+                                          ctypes.POINTER(_P), _P, _F, _F, ctypes.POINTER(_P),
+                                          ctypes.POINTER(_P), ctypes.POINTER(_P),
+                                          ctypes.POINTER(_P), _I64, _I64, _INT, _INT, _P]),
     "mach_allreduce_residual_rmsnorm_mxfp8": (_INT, [_P, _P, _P, _P, _F, _F, _P, _P, _P, _P, _I64,
                                                      _I64, _INT, _P]),
     "mach_mx_gemm_reduce_scatter": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _P]),
@@ -64,7 +74,7 @@ _SIGNATURES = {
     "mach_tune_set": (_INT, [ctypes.c_char_p, _INT]),
     "mach_tune_get": (_INT, [ctypes.c_char_p]),
 }
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 
 def exported_symbols() -> list[str]:
@@ -218,6 +228,26 @@ def interleave_gate_up(t: torch.Tensor) -> torch.Tensor:
     return out
 
 
+class _DevicePointer:
+    """Adapter that lets torch.as_tensor alias raw device memory (CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 2}
+
+
+def tensor_from_ptr(ptr: int, shape, dtype: torch.dtype, device) -> torch.Tensor:
+    """A tensor that aliases `ptr` (memory owned by the library, e.g. an all-reduce buffer).
+    The caller keeps the owner alive for as long as the tensor is used."""
+    numel = 1
+    for d in shape:
+        numel *= int(d)
+    nbytes = numel * torch.empty((), dtype=dtype).element_size()
+    with torch.cuda.device(device):
+        flat = torch.as_tensor(_DevicePointer(ptr, max(nbytes, 1)), device=torch.device(device))
+    return flat[:nbytes].view(dtype).view(*shape)
+
+
 def mx_gemm(a_codes, a_scales, w, w_scales, fmt: str = "e4m3", out: torch.Tensor | None = None,
             layout: int = LAYOUT_ROWS):
     """BF16 [M, N] = dq(A) dq(W)^T. W: [N, K] E4M3 bytes or [N, 3K/4] packed 6-bit."""
@@ -234,6 +264,8 @@ def mx_gemm(a_codes, a_scales, w, w_scales, fmt: str = "e4m3", out: torch.Tensor
         raise ValueError("scale buffer is too small")
     if out is None:
         out = torch.empty((m, n), dtype=torch.bfloat16, device=a_codes.device)
+    elif out.shape != (m, n) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous BF16 [M, N] tensor")
     with torch.cuda.device(a_codes.device):
         _check(lib().mach_mx_gemm(_ptr(a_codes), _ptr(a_scales), _ptr(w), _ptr(w_scales), _ptr(out),
                                   m, n, k, f, layout, _stream(a_codes)), "mx_gemm")
