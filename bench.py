@@ -14,7 +14,7 @@ host->device and device->host copies inside the timed region.
 
 `--impl reference` times the reference's own CPU statement of the path (quantise ->
 dequantise -> FP32 matmul -> BF16, tests/native_mxfp6/test_mxfp8_sm120.py:53-57 of the
-reference, restated in oracle/mx_oracle.py) on the host cores, on a bounded token sample.
+reference, restated in oracle/mx_oracle.py) on the host cores, at the GPU arm's batch size.
 """
 from __future__ import annotations
 
@@ -39,12 +39,21 @@ HEADLINE_M = 4096
 SWEEP_M = (1, 8, 16, 64, 256, 1024, 4096)
 EPS = 1e-6
 NUM_WEIGHT_SETS = 4       # 4 x 77 MB > 126 MB L2: weights always come from HBM
-CPU_SAMPLE_TOKENS = 1024
+CPU_SAMPLE_TOKENS = HEADLINE_M   # the CPU arm runs the GPU arm's configuration
 SOAK_SECONDS = 1.0
-# DRAM bytes (read + write) of one launch of the dominant kernel at the headline batch on one
-# GPU, from an ncu capture of `bench.py --kernel-only gate_up_swiglu` (profiles/ holds the
-# summary). Keyed by batch size.
-NCU_TRAFFIC_BYTES = {4096: 96.407296e6 + 23.392512e6}
+KERNEL_TIMING_LAUNCHES = 200     # launches of the dominant kernel timed one by one
+OWNER_MIN_BYTES = 256 << 10      # tensor-parallel payloads above this take the owner form
+TRAFFIC_FILE = ROOT / "profiles" / "ncu_traffic.json"
+
+
+def ncu_traffic(kernel: str, tokens: int):
+    """DRAM bytes (read + write) per launch from the committed profiler capture of
+    `bench.py --kernel-only <kernel> --tokens <tokens>`, with where it came from."""
+    try:
+        entry = json.loads(TRAFFIC_FILE.read_text())[kernel][str(tokens)]
+        return entry["dram_read_bytes"] + entry["dram_write_bytes"], entry["source"]
+    except (OSError, KeyError, ValueError):
+        return None, None
 
 
 def measured_peaks():
@@ -120,41 +129,194 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ GPU arm
-def make_weights(device, world, rank, seed):
-    """Synthetic MXFP8 weights with the checkpoint's shapes: BF16 ~N(0, 0.02) quantised to
-    E4M3 codes + E8M0 per 1x32 on the device. Returns MxMlpWeights of this rank's shard."""
+def make_weights(device, world, rank, seed, hidden=HIDDEN, inter=INTER, fmt="e4m3", sigma=0.02,
+                 logical=False):
+    """Synthetic weights with the checkpoint's shapes: BF16 ~N(0, sigma) quantised on the
+    device (E4M3 codes + E8M0 per 1x32; for the 6-bit formats the E4M3 codes are replaced by
+    seeded random 6-bit codes, timing only). Returns MxMlpWeights of this rank's shard; with
+    `logical` also the shard's checkpoint-layout tensors (codes, scales) of both matrices."""
     from mach_b200 import native
     from mach_b200.mlp import MxMlpWeights
-    start, count = shard_blocks(INTER, world, rank)
+    start, count = shard_blocks(inter, world, rank)
     g = torch.Generator(device=device).manual_seed(seed)
-    w_gu = (torch.randn(2 * INTER, HIDDEN, generator=g, device=device) * 0.02).to(torch.bfloat16)
-    w_d = (torch.randn(HIDDEN, INTER, generator=g, device=device) * 0.02).to(torch.bfloat16)
+    w_gu = (torch.randn(2 * inter, hidden, generator=g, device=device) * sigma).to(torch.bfloat16)
+    w_d = (torch.randn(hidden, inter, generator=g, device=device) * sigma).to(torch.bfloat16)
     gate = w_gu[start:start + count]
-    up = w_gu[INTER + start:INTER + start + count]
+    up = w_gu[inter + start:inter + start + count]
     shard_gu = torch.cat([gate, up], 0).contiguous()
     shard_d = w_d[:, start:start + count].contiguous()
+    del w_gu, w_d
     c_gu, s_gu = native.quantize_mxfp8(shard_gu)
     c_d, s_d = native.quantize_mxfp8(shard_d)
-    return MxMlpWeights.from_logical(
-        c_gu, native.unpack_scales(s_gu, shard_gu.shape[0], HIDDEN), c_d,
-        native.unpack_scales(s_d, HIDDEN, count), HIDDEN)
+    l_gu = native.unpack_scales(s_gu, shard_gu.shape[0], hidden)
+    l_d = native.unpack_scales(s_d, hidden, count)
+    if fmt != "e4m3":
+        c_gu = torch.randint(0, 256, (2 * count, hidden * 3 // 4), dtype=torch.uint8, device=device,
+                             generator=g)
+        c_d = torch.randint(0, 256, (hidden, count * 3 // 4), dtype=torch.uint8, device=device,
+                            generator=g)
+    weights = MxMlpWeights.from_logical(c_gu, l_gu, c_d, l_d, hidden, fmt=fmt)
+    if logical:
+        return weights, (c_gu, l_gu, c_d, l_d)
+    return weights
 
 
-def gemm_flops(m, inter_local):
-    return 2.0 * m * (2 * inter_local) * HIDDEN + 2.0 * m * HIDDEN * inter_local
+def gemm_flops(m, inter_local, hidden=HIDDEN):
+    return 2.0 * m * (2 * inter_local) * hidden + 2.0 * m * hidden * inter_local
 
 
-def mlp_bytes(m, inter_local):
+def mlp_bytes(m, inter_local, hidden=HIDDEN, weight_bytes=1.0):
     """Algorithmic HBM bytes of one MLP pass: weights + scales once, activations in,
     FP8 intermediate written and read once, BF16 output."""
-    w = 2 * inter_local * HIDDEN * (1 + 1 / 32) + HIDDEN * inter_local * (1 + 1 / 32)
-    return w + m * HIDDEN * 2 + 2 * m * inter_local * (1 + 1 / 32) + m * HIDDEN * 2
+    w = 3 * inter_local * hidden * (weight_bytes + 1 / 32)
+    return w + m * hidden * 2 + 2 * m * inter_local * (1 + 1 / 32) + m * hidden * 2
+
+
+def bf16_ulps(a: torch.Tensor, b: torch.Tensor) -> int:
+    """Largest distance between two BF16 tensors in units in the last place."""
+    def key(t):
+        bits = t.contiguous().view(torch.int16).to(torch.int32) & 0xFFFF
+        return torch.where(bits >= 0x8000, 0x8000 - bits, bits)
+    return int((key(a) - key(b)).abs().max()) if a.numel() else 0
+
+
+def tp_step(x, residual, residual_rows, gamma, w, group, owner):
+    """One MLP block. Tensor-parallel payloads above OWNER_MIN_BYTES keep the residual stream
+    and the BF16 norm row-owned and replicate the MXFP8 codes (owner form); smaller ones, and
+    one GPU, return norm and residual for all rows."""
+    from mach_b200.mlp import mlp_block, mlp_block_owner
+    if owner or group is None:
+        codes, scales, res_rows, norm_rows = mlp_block_owner(x, residual_rows, gamma, EPS, w, group)
+        return norm_rows, (codes, scales, res_rows)
+    norm, res = mlp_block(x, residual, gamma, EPS, w, group)
+    return norm, (res,)
+
+
+def tp_parity(group, world, rank, device, tokens):
+    """Checker leg, outside every timed region: the tensor-parallel block on `tokens` seeded
+    rows against the CPU oracle. (1) the fused reduce vs the oracle's rank-order sum +
+    residual + norm over the ranks' gathered partial sums: residual_out bit-equal, norm within
+    one BF16 ulp, codes and scales equal to the oracle quantiser applied to the kernel's own
+    norm; (2) relative Frobenius error of the normalised output against the oracle's UNSHARDED
+    MLP (quantise -> dequantise -> FP32 matmul path) on a row sample."""
+    import torch.distributed as dist
+    from mach_b200 import collective, native
+    from mach_b200.mlp import mlp_forward
+    from oracle import mx_oracle as ora   # checker only
+    g = torch.Generator().manual_seed(4242 + tokens)
+    x = torch.randn(tokens, HIDDEN, generator=g).to(torch.bfloat16).to(device)
+    residual = torch.randn(tokens, HIDDEN, generator=g).to(torch.bfloat16).to(device)
+    gamma = (0.1 * torch.randn(HIDDEN, generator=g)).to(torch.bfloat16).to(device)
+    w, (c_gu, l_gu, c_d, l_d) = make_weights(device, world, rank, 1000, logical=True)
+    partial = mlp_forward(x, w)
+    owner = tokens * HIDDEN * 2 > OWNER_MIN_BYTES
+    first, count = collective.owner_rows(tokens, group)
+    if owner:
+        norm_rows, (codes, scales, res_rows) = tp_step(
+            x, residual, residual[first:first + count].contiguous(), gamma, w, group, True)
+        norm = collective.gather_owned_rows(norm_rows, tokens, group)
+        res = collective.gather_owned_rows(res_rows, tokens, group)
+    else:
+        norm, res, codes, scales = collective.allreduce_add_rmsnorm(
+            partial, residual, gamma, EPS, group, want_quant=True)
+    torch.cuda.synchronize()
+    status = native.device_status()
+    parts = [torch.empty_like(partial) for _ in range(world)] if rank == 0 else None
+    dist.gather(partial, parts, dst=0, group=group)
+    # full checkpoint-layout weights on rank 0: gate rows | up rows, down columns by shard
+    half = c_gu.shape[0] // 2
+    mine = [t.cpu() for t in (c_gu[:half], c_gu[half:], l_gu[:half], l_gu[half:], c_d, l_d)]
+    shards = [None] * world if rank == 0 else None
+    dist.gather_object(mine, shards, dst=0, group=group)
+    if rank != 0:
+        return None
+    ref_norm, ref_res = ora.allreduce_rmsnorm([p.cpu() for p in parts], residual.cpu(),
+                                              gamma.cpu(), EPS)
+    ref_codes, ref_scales = ora.quantize_mxfp8(norm.cpu())
+    gate_c, up_c, gate_s, up_s = (torch.cat([sh[i] for sh in shards], 0) for i in range(4))
+    down_c, down_s = (torch.cat([sh[i] for sh in shards], 1) for i in (4, 5))
+    rows = torch.randperm(tokens, generator=g)[:32]
+    a_c, a_s = ora.quantize_mxfp8(x.cpu()[rows])
+    w_gu = ora.dequantize_mx(torch.cat([gate_c, up_c], 0).view(torch.uint8),
+                             torch.cat([gate_s, up_s], 0))
+    h_c, h_s = ora.swiglu_quantize(ora.mx_gemm(a_c, a_s, w_gu))
+    y = ora.mx_gemm(h_c, h_s, ora.dequantize_mx(down_c.view(torch.uint8), down_s))
+    full_norm, _ = ora.allreduce_rmsnorm([y], residual.cpu()[rows], gamma.cpu(), EPS)
+    got = norm.cpu()[rows].float()
+    return {
+        "n": world, "tokens": tokens, "form": "owner" if owner else "push",
+        "residual_equal": bool(torch.equal(res.cpu().view(torch.int16), ref_res.view(torch.int16))),
+        "norm_max_ulp": bf16_ulps(norm.cpu(), ref_norm),
+        "codes_equal": bool(torch.equal(codes.view(torch.uint8).cpu(), ref_codes)
+                            and torch.equal(ora.unswizzle_scales(scales.cpu(), tokens, HIDDEN),
+                                            ref_scales)),
+        "rel_fro_vs_unsharded_oracle": float((got - full_norm.float()).norm()
+                                             / full_norm.float().norm()),
+        "device_status": status,
+    }
+
+
+def fp8_library_peak(device):
+    """cuBLASLt through torch on this box: per-tensor-scaled E4M3 8192^3 (burst = best of 10,
+    sustained = back to back for ~1.5 s) and, where the installed torch accepts it, the MXFP8
+    block-scaled form at the two shapes of the benchmarked MLP."""
+    import torch.nn.functional as F
+    out = {}
+
+    def time_fn(fn, flops, seconds):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        reps = max(10, int(seconds * 1e3 / best))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return flops / (best * 1e-3) / 1e12, flops * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12
+
+    try:
+        n = 8192
+        a = torch.randn(n, n, device=device).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=device).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=device)
+        burst, sustained = time_fn(lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one,
+                                                            out_dtype=torch.bfloat16),
+                                   2.0 * n ** 3, 1.5)
+        out["e4m3_tensorwise_8192"] = {"burst": round(burst, 1), "sustained": round(sustained, 1)}
+    except Exception as error:  # noqa: BLE001
+        out["e4m3_tensorwise_8192"] = {"error": str(error)[:160]}
+    for name, (m, n, k) in (("mxfp8_gate_up_4096x19456x2560", (HEADLINE_M, 2 * INTER, HIDDEN)),
+                            ("mxfp8_down_4096x2560x9728", (HEADLINE_M, HIDDEN, INTER))):
+        try:
+            a = torch.randn(m, k, device=device).to(torch.float8_e4m3fn)
+            b = torch.randn(n, k, device=device).to(torch.float8_e4m3fn).t()
+            sa = torch.full((((m + 127) // 128) * 128 * ((k // 32 + 3) // 4) * 4,), 1.0,
+                            device=device).to(torch.float8_e8m0fnu)
+            sb = torch.full((((n + 127) // 128) * 128 * ((k // 32 + 3) // 4) * 4,), 1.0,
+                            device=device).to(torch.float8_e8m0fnu)
+            fn = lambda: F.scaled_mm(a, b, sa, F.ScalingType.BlockWise1x32, sb,  # noqa: E731
+                                     F.ScalingType.BlockWise1x32,
+                                     swizzle_a=F.SwizzleType.SWIZZLE_32_4_4,
+                                     swizzle_b=F.SwizzleType.SWIZZLE_32_4_4,
+                                     output_dtype=torch.bfloat16)
+            burst, sustained = time_fn(fn, 2.0 * m * n * k, 0.5)
+            out[name] = {"burst": round(burst, 1), "sustained": round(sustained, 1)}
+        except Exception as error:  # noqa: BLE001
+            out[name] = {"error": str(error)[:160]}
+    return out
 
 
 def run_gpu(args):
     import torch.distributed as dist
-    from mach_b200 import native
-    from mach_b200.mlp import mlp_block, mlp_forward
+    from mach_b200 import collective, native
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -172,15 +334,19 @@ def run_gpu(args):
     peaks = measured_peaks()
     m = args.tokens
     _, inter_local = shard_blocks(INTER, world, rank)
+    owner = world > 1 and not args.no_owner and m * HIDDEN * 2 > OWNER_MIN_BYTES
 
     sets = [make_weights(device, world, rank, 1000 + i) for i in range(NUM_WEIGHT_SETS)]
     g = torch.Generator(device=device).manual_seed(7)
     xs = [torch.randn(m, HIDDEN, generator=g, device=device).to(torch.bfloat16) for _ in range(4)]
     residual = torch.randn(m, HIDDEN, generator=g, device=device).to(torch.bfloat16)
     gamma = (0.1 * torch.randn(HIDDEN, generator=g, device=device)).to(torch.bfloat16)
+    first, count = collective.owner_rows(m, group)
+    residual_rows = residual[first:first + count].contiguous()
 
     def step(i):
-        return mlp_block(xs[i % 4], residual, gamma, EPS, sets[i % NUM_WEIGHT_SETS], group)
+        return tp_step(xs[i % 4], residual, residual_rows, gamma, sets[i % NUM_WEIGHT_SETS], group,
+                       owner)
 
     def barrier():
         if world > 1:
@@ -223,14 +389,15 @@ def run_gpu(args):
     ms = start.elapsed_time(end)
     assert torch.isfinite(out[0].float()).all()
 
-    # ---- dominant kernel (gate_up GEMM with the SwiGLU epilogue), CUDA events on its stream
+    # ---- dominant kernel (gate_up GEMM with the SwiGLU epilogue): every launch timed with its
+    # own pair of CUDA events on its stream; median and spread over KERNEL_TIMING_LAUNCHES
     codes, scales = native.quantize_mxfp8(xs[0])
     evs = []
     for i in range(args.warmup):
         native.mx_gemm_swiglu(codes, scales, sets[i % NUM_WEIGHT_SETS].w_gate_up,
                               sets[i % NUM_WEIGHT_SETS].s_gate_up, layout=native.LAYOUT_GATE_UP_32)
     torch.cuda.synchronize()
-    for i in range(args.steps):
+    for i in range(KERNEL_TIMING_LAUNCHES):
         w = sets[i % NUM_WEIGHT_SETS]
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -239,17 +406,19 @@ def run_gpu(args):
         e1.record()
         evs.append((e0, e1))
     torch.cuda.synchronize()
-    k_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    k_all = sorted(a.elapsed_time(b) for a, b in evs)
+    k_ms = statistics.median(k_all)
+    k_mean = statistics.mean(k_all)
+    k_p10, k_p90 = k_all[len(k_all) // 10], k_all[(len(k_all) * 9) // 10]
 
     # ---- end to end through the public API with host buffers. Every step copies its input
     # from pinned host memory and its result back; the three legs run on their own streams
     # (double-buffered), so step i+1's upload and step i-1's download overlap step i's kernels,
     # as a serving engine would pipeline them. PCIe is full duplex. With N ranks each rank
-    # uploads 1/N of the token rows and the ranks all-gather them over NVLink (the activations
-    # of a tensor-parallel layer are replicated), and each rank downloads 1/N of the result, so
-    # the bytes crossing PCIe per step do not grow with N.
-    rows_lo = (m * rank) // world
-    rows_hi = (m * (rank + 1)) // world
+    # uploads the token rows it owns and the ranks all-gather them over NVLink (the activations
+    # of a tensor-parallel layer are replicated), and each rank downloads the rows of the
+    # result it owns, so the bytes crossing PCIe per step do not grow with N.
+    rows_lo, rows_hi = first, first + count
     host_in = [torch.randn(m, HIDDEN).to(torch.bfloat16).pin_memory() for _ in range(2)]
     host_out = [torch.empty((m, HIDDEN), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     dev_in = [torch.empty((m, HIDDEN), dtype=torch.bfloat16, device=device) for _ in range(2)]
@@ -262,10 +431,10 @@ def run_gpu(args):
     ev_out = [torch.cuda.Event() for _ in range(2)]      # download into host buffer b finished
     keep = [None, None]
 
-    def e2e_steps(count):
+    def e2e_steps(count_steps):
         for st in (s_in, s_run, s_out):
             st.wait_stream(main)
-        for i in range(count):
+        for i in range(count_steps):
             b = i % 2
             with torch.cuda.stream(s_in):
                 if i >= 2:
@@ -278,7 +447,9 @@ def run_gpu(args):
                 ev_in[b].record(s_in)
             with torch.cuda.stream(s_run):
                 s_run.wait_event(ev_in[b])
-                norm, _ = mlp_block(dev_in[b], residual, gamma, EPS, sets[i % NUM_WEIGHT_SETS], group)
+                result = tp_step(dev_in[b], residual, residual_rows, gamma,
+                                 sets[i % NUM_WEIGHT_SETS], group, owner)
+                norm = result[0]
                 ev_free[b].record(s_run)
                 ev_done[b].record(s_run)
             with torch.cuda.stream(s_out):
@@ -286,12 +457,14 @@ def run_gpu(args):
                 if i >= 2:
                     s_out.wait_event(ev_out[b])
                 norm.record_stream(s_out)
-                if even_split:
+                if owner:
+                    host_out[b][rows_lo:rows_hi].copy_(norm, non_blocking=True)
+                elif even_split:
                     host_out[b][rows_lo:rows_hi].copy_(norm[rows_lo:rows_hi], non_blocking=True)
                 else:
                     host_out[b].copy_(norm, non_blocking=True)
                 ev_out[b].record(s_out)
-                keep[b] = norm
+                keep[b] = result
         for st in (s_in, s_run, s_out):
             main.wait_stream(st)
 
@@ -311,10 +484,24 @@ def run_gpu(args):
     ms, e2e_ms, k_ms = times.tolist()
     status = native.device_status()
 
+    # ---- checker leg (N >= 2): the tensor-parallel block against the CPU oracle
+    parity = None
+    if world > 1 and not args.no_parity:
+        parity = [tp_parity(group, world, rank, device, t) for t in (32, 512, HEADLINE_M)]
+
+    # ---- the other tensor-parallel configurations (MXFP6 MLP, expert-parallel MoE)
+    tp_suite = None
+    if not args.no_tp_suite:
+        tp_suite = run_tp_suite(group, world, rank, device, peaks)
+
     # ---- batch sweep under CUDA graphs (decode sizes are launch-bound otherwise), 1 GPU only
     sweep = None
     if world == 1 and not args.no_sweep:
         sweep = run_sweep(device, sets, gamma, peaks, args)
+
+    library = None
+    if world == 1 and rank == 0 and not args.no_library:
+        library = fp8_library_peak(device)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -324,6 +511,26 @@ def run_gpu(args):
         flops = 2.0 * m * (2 * inter_local) * HIDDEN
         achieved = flops / (k_ms * 1e-3) / 1e12
         peak = 2.0 * peaks["bf16_tflops_sustained"]
+        traffic, traffic_source = ncu_traffic("gate_up_swiglu", m) if world == 1 else (None, None)
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                    "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_source,
+                    "kernel": "mx_gemm_pair_kernel<SwiGLU> (gate_up + SwiGLU + MXFP8 "
+                              "requant, cta_group::2, 256 x 192 tiles)",
+                    "kernel_ms": k_ms,
+                    "kernel_ms_stats": {"launches": KERNEL_TIMING_LAUNCHES, "median": k_ms,
+                                        "mean": k_mean, "p10": k_p10, "p90": k_p90},
+                    "frac_of_burst_peak": achieved / (2.0 * peaks["bf16_tflops"]),
+                    "peak_note": f"2 x bf16_tflops_sustained ({peaks['source']}): FP8 issues "
+                                 "at twice the BF16 rate; frac_of_burst_peak uses 2 x bf16_tflops"}
+        if library is not None:
+            roofline["fp8_library_tflops"] = library
+            ref = library.get("mxfp8_gate_up_4096x19456x2560", {})
+            if "sustained" in ref:
+                roofline["vs_library_mxfp8_gate_up"] = achieved / ref["sustained"]
+        outputs = ("MXFP8 codes + scales replicated; BF16 norm and residual stream row-owned "
+                   "(1/N of the rows per rank)") if owner else \
+                  "BF16 norm + residual (all rows)" if world > 1 else \
+                  "BF16 norm + residual + MXFP8 codes + scales"
         line = {
             "metric": "mlp_layer_tokens_per_s", "value": m * args.steps / (ms * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -332,31 +539,149 @@ def run_gpu(args):
             "data": "synthetic",
             "config": {"workload": "MXFP8 dense decoder MLP block, hidden 2560, intermediate 9728",
                        "tokens": m, "parallelism": f"tp{world}", "soak_steps": soak_steps,
+                       "reduce": "owner form" if owner else ("push form" if world > 1 else "none"),
+                       "step_outputs": outputs,
                        "l2": f"rotates {NUM_WEIGHT_SETS} weight sets "
                              f"({NUM_WEIGHT_SETS * sets[0].nbytes() * world / 1e6:.0f} MB > 126 MB L2)"},
             "e2e": {"value": m * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": m * HIDDEN * 2, "d2h_bytes_per_step": m * HIDDEN * 2,
-                    "note": "bytes over all ranks; each rank moves 1/N of the rows and the "
+                    "note": "bytes over all ranks; each rank moves the rows it owns and the "
                             "ranks all-gather the input over NVLink" if world > 1 else
                             "upload, kernels and download on three streams, double-buffered"},
             "gpu_launches": 4 * args.steps,
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES.get(m) if world == 1 else None,
-                         "kernel": "mx_gemm_pair_kernel<SwiGLU> (gate_up + SwiGLU + MXFP8 "
-                                   "requant, cta_group::2, 256 x 192 tiles)",
-                         "kernel_ms": k_ms,
-                         "peak_note": f"2 x bf16_tflops_sustained ({peaks['source']}): FP8 issues "
-                                      "at twice the BF16 rate"},
+            "roofline": roofline,
             "clocks": clocks, "device_status": status,
         }
+        if parity is not None:
+            line["parity"] = parity
+        if tp_suite is not None:
+            line["tp_suite"] = tp_suite
         if sweep is not None:
             line["sweep"] = sweep
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
         print(json.dumps(line))
     if world > 1:
+        collective.close_all()
         dist.destroy_process_group()
+
+
+def run_tp_suite(group, world, rank, device, peaks):
+    """The other configurations that shard over N GPUs, per batch: the MXFP6 (E2M3) MLP, hidden
+    5120 / intermediate 17408, gate_up column- and down row-parallel with the fused reduce, and
+    the 256-expert top-8 MoE (hidden 2048, intermediate 512, E2M3) with the experts split N
+    ways and the same fused reduce over the combined output. CUDA-graph replays, CUDA events,
+    max over ranks. Random 6-bit codes with oracle-like scales (timing only)."""
+    import torch.distributed as dist
+    from mach_b200 import collective, native
+    from mach_b200 import moe as moe_mod
+    from mach_b200.mlp import mlp_block, mlp_block_owner
+    out = []
+    g = torch.Generator(device=device).manual_seed(21)
+
+    def timed(fn, variants, calls):
+        try:
+            us = graph_time_us(fn, variants, calls=calls, reps=5)
+        except RuntimeError:
+            # a launch that cannot be captured: time the same calls eagerly
+            torch.cuda.synchronize()
+            for i in range(3):
+                fn(i)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for i in range(calls * 3):
+                fn(i)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (calls * 3)
+        t = torch.tensor([us], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    # ---- MXFP6 dense MLP, tensor parallel
+    hid, inter = 5120, 17408
+    _, inter_local = shard_blocks(inter, world, rank)
+    n_sets = 2 if world == 1 else max(2, min(8, (2 * world)))   # > L2 in total on every rank
+    sets = [make_weights(device, world, rank, 3000 + i, hid, inter, "e2m3", 0.015)
+            for i in range(n_sets)]
+    gamma = (0.1 * torch.randn(hid, generator=g, device=device)).to(torch.bfloat16)
+    for m in (1, 32, 512, 4096):
+        x = torch.randn(m, hid, generator=g, device=device).to(torch.bfloat16)
+        residual = torch.randn(m, hid, generator=g, device=device).to(torch.bfloat16)
+        owner = world > 1 and m * hid * 2 > OWNER_MIN_BYTES
+        first, count = collective.owner_rows(m, group)
+        rows = residual[first:first + count].contiguous()
+        if owner:
+            fn = lambda i: mlp_block_owner(x, rows, gamma, EPS, sets[i % n_sets], group)  # noqa: E731
+        else:
+            fn = lambda i: mlp_block(x, residual, gamma, EPS, sets[i % n_sets], group)  # noqa: E731
+        us = timed(fn, n_sets, 10)
+        flops = 2.0 * m * 3 * hid * inter              # whole job, all ranks
+        nbytes = mlp_bytes(m, inter_local, hid, 0.75)   # per rank
+        out.append({"config": "mxfp6_e2m3_mlp_h5120_i17408", "tp": world, "tokens": m,
+                    "reduce": "owner" if owner else ("push" if world > 1 else "none"),
+                    "us": round(us, 2), "tokens_per_s": m / (us * 1e-6),
+                    "tflops_per_gpu": round(flops / world / (us * 1e-6) / 1e12, 1),
+                    "hbm_gbs_per_gpu": round(nbytes / (us * 1e-6) / 1e9, 1),
+                    "frac_hbm_measured": round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 3),
+                    "frac_fp8_measured": round(flops / world / (us * 1e-6) / 1e12
+                                               / (2 * peaks["bf16_tflops_sustained"]), 3)})
+    del sets
+    torch.cuda.empty_cache()
+
+    # ---- MoE, expert parallel
+    e, hid, inter, top_k = 256, 2048, 512, 8
+    per = e // world
+    w13 = torch.randint(0, 256, (per, 2 * inter, hid * 3 // 4), dtype=torch.uint8, device=device,
+                        generator=g)
+    s13 = torch.randint(116, 120, (per, 2 * inter, hid // 32), dtype=torch.uint8, device=device,
+                        generator=g)
+    w2 = torch.randint(0, 256, (per, hid, inter * 3 // 4), dtype=torch.uint8, device=device,
+                       generator=g)
+    s2 = torch.randint(116, 120, (per, hid, inter // 32), dtype=torch.uint8, device=device,
+                       generator=g)
+    weights = moe_mod.MoeWeights.from_logical(w13, s13, w2, s2, fmt="e2m3")
+    del w13, s13, w2, s2
+    expert_map = None
+    if world > 1:
+        expert_map = torch.full((e,), -1, dtype=torch.int32, device=device)
+        expert_map[rank * per:(rank + 1) * per] = torch.arange(per, dtype=torch.int32, device=device)
+    gamma = (0.1 * torch.randn(hid, generator=g, device=device)).to(torch.bfloat16)
+    per_expert = 3 * hid * inter * (0.75 + 1 / 32)
+    for m in (1, 64, 1024, 4096):
+        gen = torch.Generator(device=device).manual_seed(77 + m)   # same tokens on every rank
+        x = torch.randn(m, hid, generator=gen, device=device).to(torch.bfloat16)
+        logits = torch.randn(m, e, generator=gen, device=device).to(torch.bfloat16)
+        residual = torch.randn(m, hid, generator=gen, device=device).to(torch.bfloat16)
+        _, ids = moe_mod.router_topk(logits, top_k)
+        local_ids = ids[(ids // per) == rank] if world > 1 else ids
+        distinct = int(torch.unique(local_ids).numel())
+        owner = world > 1 and m * hid * 2 > OWNER_MIN_BYTES
+        first, count = collective.owner_rows(m, group)
+        rows = residual[first:first + count].contiguous()
+
+        def fn(i):
+            tw, ti = moe_mod.router_topk(logits, top_k)
+            partial = moe_mod.experts_forward(x, weights, tw, ti, expert_map)
+            if world == 1:
+                return native.add_rmsnorm_mxfp8(partial, residual, gamma, EPS)
+            if owner:
+                return collective.allreduce_owner_add_rmsnorm(partial, rows, gamma, EPS, group, m)
+            return collective.allreduce_add_rmsnorm(partial, residual, gamma, EPS, group,
+                                                    want_quant=True)
+        us = timed(fn, 1, 10)
+        nbytes = distinct * per_expert + m * hid * 4
+        flops = 2.0 * m * top_k * 3 * hid * inter
+        out.append({"config": "moe_e256_top8_h2048_i512_e2m3", "ep": world, "tokens": m,
+                    "reduce": "owner" if owner else ("push" if world > 1 else "none"),
+                    "distinct_local_experts": distinct, "us": round(us, 2),
+                    "tokens_per_s": m / (us * 1e-6),
+                    "tflops_per_gpu": round(flops / world / (us * 1e-6) / 1e12, 1),
+                    "hbm_gbs_per_gpu": round(nbytes / (us * 1e-6) / 1e9, 1),
+                    "frac_hbm_measured": round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 3)})
+    return out
 
 
 def run_kernel_only(args, xs, sets, device):
@@ -659,6 +984,12 @@ def main():
     ap.add_argument("--tokens", type=int, default=HEADLINE_M)
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check at N >= 2")
+    ap.add_argument("--no-tp-suite", action="store_true",
+                    help="skip the MXFP6 MLP / MoE tensor-parallel timings")
+    ap.add_argument("--no-library", action="store_true", help="skip the cuBLASLt FP8 peak")
+    ap.add_argument("--no-owner", action="store_true",
+                    help="N >= 2: push-form reduce with all rows on every rank")
     ap.add_argument("--suite", default=None,
                     help="'all' or a comma list of c1,c2,c3,c4,c5: per-config timings, one JSON "
                          "line per case, instead of the headline step")

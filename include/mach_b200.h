@@ -334,7 +334,8 @@ MACH_API int mach_moe_combine(const void* y_bf16, const void* topk_weights_f32,
  * feature-major, <= 64), "smem_cap_kb" (cap on dynamic shared memory per CTA), "tm_min_m"
  * (smallest batch for the persistent 256-token kernels), "tm_bn" (their tile width), "pair"
  * (0: single-CTA persistent kernel instead of the cta_group::2 kernel), "panel_m"
- * (raster panel height), "debug" (experiment bits; results are wrong when set).
+ * (raster panel height). A library built with -DMACH_EXPERIMENTS (kernel sweeps only) also
+ * takes experiment bits that switch parts of the MMA loops off; the default build has none.
  * No counterpart in the reference (its tile table is torch.ops.mxfp6.set_w6a8_config,
  * src/vllm_mach/mxfp6/moe_projection.py:35-105, an SM120 table). */
 MACH_API int mach_tune_set(const char* name, int value);

@@ -60,3 +60,31 @@ def test_static_scratch_refuses_oversized_problems():
         m, n, k, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == 2
     assert b"exceeds the built-in scratch" in lib.mach_last_error()
+
+
+def test_static_scratch_at_its_limit():
+    """A problem that fills the built-in array almost completely (16 x 51 x 2560 x 4 B =
+    8 355 840 of 8 388 608 bytes) must still match the caller-scratch route bit for bit, and
+    one row more (8 519 680 bytes) must be refused: the accept/refuse boundary sits where the
+    header says it does, and a nearly full array does not overrun."""
+    from mach_b200 import native
+    lib = native.lib()
+    n, k = 2560, 2048
+    b, sb = _weight(n, k, 3)
+    b, sb = b.cuda(), sb.cuda()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for m, accepted in ((51, True), (52, False)):
+        x = randn_bf16(m, k, 20 + m)
+        q, sa = native.fp8_group_quantize(x.cuda())
+        out = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+        rc = lib.mach_block_fp8_gemm_ordered_static(
+            q.data_ptr(), b.data_ptr(), sa.data_ptr(), sb.data_ptr(), out.data_ptr(), m, n, k, stream)
+        if not accepted:
+            assert rc == 2 and b"exceeds the built-in scratch" in lib.mach_last_error()
+            continue
+        assert rc == 0, lib.mach_last_error().decode()
+        raw = torch.empty((k // 128, m, n), dtype=torch.float32, device="cuda")
+        expected = native.block_fp8_gemm(q, sa, b, sb, raw=raw)
+        torch.cuda.synchronize()
+        assert native.device_status() == 0
+        assert torch.equal(out.view(torch.int16), expected.view(torch.int16))

@@ -345,7 +345,8 @@ template <bool kSwap>
 int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, BlockFp8Params& prm, dim3 grid,
            int smem_bytes, cudaStream_t stream) {
   auto kernel = block_fp8_gemm_kernel<kSwap>;
-  static int configured_smem = 0;
+  static int configured_smem_dev[kMaxDeviceSlots] = {};  // the attribute is per device
+  int& configured_smem = configured_smem_dev[device_slot()];
   if (smem_bytes > configured_smem) {
     const cudaError_t e =
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);

@@ -344,7 +344,8 @@ int run_block_fp8_tm(const void* a, const void* b, const float* sa, const float*
   if (rc) return rc;
 
   auto kernel = block_fp8_tm_kernel;
-  static int configured_smem = 0;
+  static int configured_smem_dev[kMaxDeviceSlots] = {};  // the attribute is per device
+  int& configured_smem = configured_smem_dev[device_slot()];
   if (smem_bytes > configured_smem) {
     const cudaError_t e =
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);

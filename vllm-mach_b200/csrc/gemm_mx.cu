@@ -239,7 +239,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     const uint32_t lo_step = (uint32_t)stage_bytes >> 4;
     const uint32_t lo_q = (uint32_t)(kNumP * kTileBytes) >> 4;
     const uint32_t lo_sf = (uint32_t)sf_off >> 4;
+#ifdef MACH_EXPERIMENTS
     const bool skip_cp = (p.debug & 1) != 0, skip_mma = (p.debug & 2) != 0;
+#else
+    constexpr bool skip_cp = false, skip_mma = false;
+#endif
     int s = 0;
     uint32_t ph = 0;
     for (int kb = kb_begin; kb < kb_end; ++kb) {
@@ -559,7 +563,8 @@ template <bool kSwap, bool kSwiglu, bool kIl>
 int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, MxGemmParams& prm, dim3 grid,
            int smem_bytes, cudaStream_t stream) {
   auto kernel = mx_gemm_kernel<kSwap, kSwiglu, kIl>;
-  static int configured_smem = 0;  // per instantiation
+  static int configured_smem_dev[kMaxDeviceSlots] = {};  // the attribute is per device
+  int& configured_smem = configured_smem_dev[device_slot()];
   if (smem_bytes > configured_smem) {
     const cudaError_t e =
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -835,7 +840,9 @@ extern "C" int mach_tune_set(const char* name, int value) {
   else if (!strcmp(name, "swap_max_m")) g_tune.swap_max_m = value;
   else if (!strcmp(name, "smem_cap_kb")) g_tune.smem_cap_kb = value;
   else if (!strcmp(name, "panel_m")) g_tune.panel_m = value;
+#ifdef MACH_EXPERIMENTS
   else if (!strcmp(name, "debug")) g_tune.debug = value;
+#endif
   else if (!strcmp(name, "moe_ctas_per_sm")) g_tune.moe_ctas_per_sm = value;
   else if (!strcmp(name, "moe_token_major")) g_tune.moe_token_major = value;
   else if (!strcmp(name, "moe_tm_min_rows")) g_tune.moe_tm_min_rows = value;

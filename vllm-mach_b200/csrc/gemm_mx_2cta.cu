@@ -291,8 +291,12 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const uint32_t lo_b2 = (uint32_t)(kABytes + b2_off) >> 4;
       const uint32_t lo_sf = (uint32_t)sf_off >> 4;
       const uint32_t sfa_tmem = tmem_base + sfa_col;
+#ifdef MACH_EXPERIMENTS
       const bool skip_mma = (p.debug & 2) != 0;
       const bool skip_cp = (p.debug & 1) != 0;
+#else
+      constexpr bool skip_mma = false, skip_cp = false;
+#endif
       int s = 0;
       uint32_t ph = 0;
       int tile_i = 0;
@@ -506,7 +510,8 @@ int launch(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& 
            const CUtensorMap& tm_sfa, const CUtensorMap& tm_sfb, const PairParams& prm, int grid, int smem_bytes,
            cudaStream_t stream) {
   auto kernel = mx_gemm_pair_kernel<kSwiglu, kTwo>;
-  static int configured_smem = 0;
+  static int configured_smem_dev[kMaxDeviceSlots] = {};  // the attribute is per device
+  int& configured_smem = configured_smem_dev[device_slot()];
   if (smem_bytes > configured_smem) {
     const cudaError_t e =
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -517,9 +522,11 @@ int launch(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& 
   }
   // A persistent grid must be resident as a whole: floor-swept GPCs can hold fewer 2-CTA
   // clusters than SMs / 2, and a cluster that starts late would serialise its whole tile list.
-  static int max_clusters = 0;
-  static int max_clusters_smem = -1;
-  if (max_clusters_smem != smem_bytes) {
+  static int max_clusters_dev[kMaxDeviceSlots] = {};
+  static int max_clusters_smem_dev[kMaxDeviceSlots] = {};   // shared memory size + 1 of the cached query
+  int& max_clusters = max_clusters_dev[device_slot()];
+  int& max_clusters_smem_plus1 = max_clusters_smem_dev[device_slot()];
+  if (max_clusters_smem_plus1 != smem_bytes + 1) {
     cudaLaunchConfig_t q = {};
     q.gridDim = dim3((unsigned)grid);
     q.blockDim = dim3(kThreads);
@@ -534,7 +541,7 @@ int launch(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& 
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) == cudaSuccess && n > 0) max_clusters = n;
     else max_clusters = sm_count() / 2;
-    max_clusters_smem = smem_bytes;
+    max_clusters_smem_plus1 = smem_bytes + 1;
   }
   grid = 2 * std::max(1, std::min(grid / 2, max_clusters));
   g_last_pairs = grid / 2;

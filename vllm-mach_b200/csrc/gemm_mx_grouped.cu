@@ -578,7 +578,8 @@ template <bool kSwiglu>
 int launch_tm(const CUtensorMap& tm_a, const CUtensorMap& tm_w, const GroupedParams& prm, int grid,
               int smem_bytes, cudaStream_t stream) {
   auto kernel = mx_grouped_tm_kernel<kSwiglu>;
-  static int configured_smem = 0;
+  static int configured_smem_dev[kMaxDeviceSlots] = {};  // the attribute is per device
+  int& configured_smem = configured_smem_dev[device_slot()];
   if (smem_bytes > configured_smem) {
     const cudaError_t e =
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -597,7 +598,8 @@ template <bool kSwiglu>
 int launch(const CUtensorMap& tm_w, const CUtensorMap& tm_a, const GroupedParams& prm, int grid,
            int smem_bytes, cudaStream_t stream) {
   auto kernel = mx_grouped_gemm_kernel<kSwiglu>;
-  static int configured_smem = 0;
+  static int configured_smem_dev[kMaxDeviceSlots] = {};  // the attribute is per device
+  int& configured_smem = configured_smem_dev[device_slot()];
   if (smem_bytes > configured_smem) {
     const cudaError_t e =
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);

@@ -300,7 +300,8 @@ template <bool kSwiglu>
 int launch(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const TmParams& prm, int grid,
            int smem_bytes, cudaStream_t stream) {
   auto kernel = mx_gemm_tm_kernel<kSwiglu>;
-  static int configured_smem = 0;
+  static int configured_smem_dev[kMaxDeviceSlots] = {};  // the attribute is per device
+  int& configured_smem = configured_smem_dev[device_slot()];
   if (smem_bytes > configured_smem) {
     const cudaError_t e =
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);

@@ -48,6 +48,12 @@ int max_smem_optin() {
   return v > 0 ? v : 232448;
 }
 
+int device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return 0;
+  return dev < kMaxDeviceSlots ? dev : kMaxDeviceSlots - 1;
+}
+
 bool pdl_enabled() { return g_pdl; }
 void set_pdl_enabled(bool on) { g_pdl = on; }
 

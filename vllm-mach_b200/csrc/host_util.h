@@ -12,6 +12,10 @@ namespace mach {
 int fail(int code, const char* fmt, ...);
 // cudaGetLastError() after a launch -> MACH_OK / MACH_ERR_CUDA.
 int check_launch(const char* what);
+// Index of the current device for per-device host caches (function attributes, occupancy
+// queries, symbol addresses are all per device), clamped to [0, kMaxDeviceSlots).
+constexpr int kMaxDeviceSlots = 64;
+int device_slot();
 // Number of SMs of the current device (cached per device).
 int sm_count();
 // Opt-in shared memory limit per block of the current device.
