@@ -1,4 +1,4 @@
-"""Fused all-reduce + residual + RMSNorm (+ MXFP8) on 2 (and 4) GPUs against the oracle's
+"""Fused all-reduce + residual + RMSNorm (+ MXFP8) on 2 (4, 8) GPUs against the oracle's
 restatement of native/ar_norm/trtllm_allreduce_fusion_mxfp8.cuh. Bar: the BF16 reduced sum
 and residual_out bit-exact (FP32 sum in rank order is order-defined), norm within one BF16
 ulp, codes/scales bit-exact given the kernel's own norm. Child processes, NVLS off."""
@@ -63,6 +63,41 @@ def _worker(rank, world, port, results):
                         failures.append(tag + " codes differ")
                     if not torch.equal(ora.unswizzle_scales(scales.cpu(), m, h), rs):
                         failures.append(tag + " scales differ")
+        # Owner form: the residual stream and the BF16 norm stay with the owner of the rows, the
+        # MXFP8 codes and scales of ALL rows reach every rank; same arithmetic, same bytes.
+        for h in (2560, 5120):
+            gamma = randn_bf16(1, h, 3, 0.1)[0].contiguous()
+            for it, m in enumerate((1, 33, 512, 4096, 1000, 512)):
+                partials = [randn_bf16(m, h, 300 * it + r + h) for r in range(world)]
+                residual = randn_bf16(m, h, 1999 + it)
+                first, count = collective.owner_rows(m, group)
+                rows = residual[first:first + count].contiguous().cuda()
+                if it % 2:
+                    target = collective.owner_partial_buffer(group, h, m, torch.device("cuda", rank))
+                    target.copy_(partials[rank].cuda())
+                    dev_partial = None
+                else:
+                    dev_partial = partials[rank].cuda()
+                codes, scales, res_rows, norm_rows = collective.allreduce_owner_add_rmsnorm(
+                    dev_partial, rows, gamma.cuda(), eps, group, m)
+                torch.cuda.synchronize()
+                ref_norm, ref_res = ora.allreduce_rmsnorm(partials, residual, gamma, eps)
+                tag = f"owner h{h} m{m} rank{rank}"
+                if native.device_status() != 0:
+                    failures.append(tag + " device wait gave up")
+                if not torch.equal(res_rows.cpu().view(torch.int16),
+                                   ref_res[first:first + count].view(torch.int16)):
+                    failures.append(tag + " residual_out rows differ")
+                own_ref = ref_norm[first:first + count].float()
+                diff = (norm_rows.float().cpu() - own_ref).abs()
+                if not bool((diff <= own_ref.abs().clamp_min(1e-30) * 2.0 ** -7).all()):
+                    failures.append(tag + f" norm off by {float(diff.max())}")
+                full_norm = collective.gather_owned_rows(norm_rows, m, group)
+                rc, rs = ora.quantize_mxfp8(full_norm.cpu())
+                if not torch.equal(codes.view(torch.uint8).cpu(), rc):
+                    failures.append(tag + " codes differ")
+                if not torch.equal(ora.unswizzle_scales(scales.cpu(), m, h), rs):
+                    failures.append(tag + " scales differ")
         # Reduce-scatter from the down projection's epilogue: same BF16 partial sums, same rank
         # order, so the whole block must equal the separate GEMM + all-reduce bit for bit.
         from mach_b200.mlp import MxMlpWeights, mlp_block
@@ -95,6 +130,25 @@ def _worker(rank, world, port, results):
                 failures.append(tag + " residual_out differs from the separate path")
             if not torch.equal(norm.view(torch.int16), base_norm.view(torch.int16)):
                 failures.append(tag + " norm differs from the separate path")
+            # the owner-form block (down projection writes into the communication buffer)
+            from mach_b200.mlp import mlp_block_owner
+            first, count = collective.owner_rows(m, group)
+            for rep in range(2):
+                codes, scales, res_rows, norm_rows = mlp_block_owner(
+                    x, residual[first:first + count].contiguous(), gamma, eps, weights, group)
+            torch.cuda.synchronize()
+            tag = f"owner block m{m} rank{rank}"
+            if native.device_status() != 0:
+                failures.append(tag + " device wait gave up")
+            if not torch.equal(res_rows.view(torch.int16),
+                               base_res[first:first + count].view(torch.int16)):
+                failures.append(tag + " residual_out differs from the push path")
+            if not torch.equal(norm_rows.view(torch.int16),
+                               base_norm[first:first + count].view(torch.int16)):
+                failures.append(tag + " norm differs from the push path")
+            base_codes, base_scales = native.quantize_mxfp8(base_norm)
+            if not torch.equal(codes.view(torch.uint8), base_codes.view(torch.uint8)):
+                failures.append(tag + " codes differ from the push path")
         collective.close_all()
     finally:
         dist.barrier()
@@ -102,7 +156,7 @@ def _worker(rank, world, port, results):
     results[rank] = failures
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_fused_allreduce_rmsnorm(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
