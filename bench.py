@@ -225,7 +225,8 @@ def tp_parity(group, world, rank, device, tokens):
     dist.gather(partial, parts, dst=0, group=group)
     # full checkpoint-layout weights on rank 0: gate rows | up rows, down columns by shard
     half = c_gu.shape[0] // 2
-    mine = [t.cpu() for t in (c_gu[:half], c_gu[half:], l_gu[:half], l_gu[half:], c_d, l_d)]
+    mine = [t.contiguous().view(torch.uint8).cpu().numpy()
+            for t in (c_gu[:half], c_gu[half:], l_gu[:half], l_gu[half:], c_d, l_d)]
     shards = [None] * world if rank == 0 else None
     dist.gather_object(mine, shards, dst=0, group=group)
     if rank != 0:
@@ -233,8 +234,9 @@ def tp_parity(group, world, rank, device, tokens):
     ref_norm, ref_res = ora.allreduce_rmsnorm([p.cpu() for p in parts], residual.cpu(),
                                               gamma.cpu(), EPS)
     ref_codes, ref_scales = ora.quantize_mxfp8(norm.cpu())
-    gate_c, up_c, gate_s, up_s = (torch.cat([sh[i] for sh in shards], 0) for i in range(4))
-    down_c, down_s = (torch.cat([sh[i] for sh in shards], 1) for i in (4, 5))
+    gate_c, up_c, gate_s, up_s = (torch.cat([torch.from_numpy(sh[i]) for sh in shards], 0)
+                                  for i in range(4))
+    down_c, down_s = (torch.cat([torch.from_numpy(sh[i]) for sh in shards], 1) for i in (4, 5))
     rows = torch.randperm(tokens, generator=g)[:32]
     a_c, a_s = ora.quantize_mxfp8(x.cpu()[rows])
     w_gu = ora.dequantize_mx(torch.cat([gate_c, up_c], 0).view(torch.uint8),

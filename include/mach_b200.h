@@ -328,6 +328,28 @@ MACH_API int mach_moe_combine(const void* y_bf16, const void* topk_weights_f32,
                               const void* pos_of, void* out_bf16, int64_t m, int64_t h,
                               int64_t topk, void* stream);
 
+/* Staged form of the layer, for callers that drive the stages themselves the way the
+ * reference's shims do (mxfp6_sm120_route / _grouped_gemm / _silu_grouped_gemm / _reduce,
+ * src/vllm_mach/mxfp6/moe_utils.py:205-488). The activation arrives already quantised:
+ * mach_moe_scatter_codes copies codes [M, K] + logical scales [M, K/32] of every token into
+ * its top-k permuted rows pos_of[token, j] (swizzled scales out). mach_moe_stage_offsets turns
+ * the route outputs into the shims' int64 pair: expert_offsets[E + 1] = routed rows before
+ * each expert (true counts), scale_offsets[E + 1] = first row of each expert's 128-row padded
+ * segment; unlike the reference, whose permuted ACTIVATION rows are unpadded, here activation
+ * and scale rows share the padded index space, so the permuted buffers need
+ * mach_moe_rows_cap rows. mach_moe_work_from_offsets rebuilds the grouped GEMM's work list
+ * from that pair on the device. */
+MACH_API int mach_moe_scatter_codes(const void* codes_in, const void* logical_scales,
+                                    const void* pos_of, int64_t m, int64_t topk, int64_t k,
+                                    void* codes, void* scales, void* stream);
+MACH_API int mach_moe_stage_offsets(const void* counts, const void* offsets, int64_t experts,
+                                    void* expert_offsets_i64, void* scale_offsets_i64,
+                                    void* stream);
+MACH_API int mach_moe_work_from_offsets(const void* expert_offsets_i64,
+                                        const void* scale_offsets_i64, int64_t experts,
+                                        int64_t chunk_rows, int64_t work_cap, void* work,
+                                        void* num_work, void* stream);
+
 /* Tuning / experiment knobs (process-global, not thread-safe; 0 restores the heuristic):
  * "split" (cluster size along K of the feature-major GEMM: 1, 2, 4, 8), "stages" (pipeline
  * depth), "bn" (token-major N tile: 128, 256), "swap_max_m" (largest batch handled

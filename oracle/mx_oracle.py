@@ -10,10 +10,15 @@ Parity pins (checked in tests/test_oracle_cpu.py against fixtures under tests/go
   * activation MXFP8 / SwiGLU / residual+RMSNorm / 1x128 FP8 quantisers and the ordered
     block-FP8 GEMM <- outputs of the reference's own Triton kernels executed on CPU with
     TRITON_INTERPRET=1 (tests/golden/make_golden.py is the generating script).
+  * all-reduce + residual + RMSNorm (+ MXFP8) <- the reference's own device code
+    (FusedOp / rms_norm / allreduce_sum / the MXFP8 branch of
+    native/ar_norm/trtllm_allreduce_fusion_mxfp8.cuh) cut out of the header where it lies and
+    compiled for the host by oracle/build_ref.py: rounding points bit for bit, the norm within
+    one BF16 ulp (summation tree), codes and scale swizzle bit for bit. Its fast-math rsqrt is
+    the one step replaced (1 / sqrt).
   * parity unpinned: the 6-bit packing order and the MXFP6 weight quantiser (they live in the
     third-party wheel mxfp6-sm120==0.3.2, Nekofish-L/mxfp6_sm120@dd9752fb, whose source is
-    not part of the reference tree); the all-reduce rounding order is restated from
-    native/ar_norm/trtllm_allreduce_fusion_mxfp8.cuh, which cannot be compiled here.
+    not part of the reference tree), and the MoE stage order for the same reason.
 
 Every function cites the reference file:line it follows (paths relative to the reference).
 """

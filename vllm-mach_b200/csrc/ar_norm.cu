@@ -381,48 +381,83 @@ __device__ __forceinline__ void owner_body(const ArParams& p, uint8_t* mine, uin
     poison = poison || late;
   }
 
-  // ---- (2) the other owners' codes and scales
+  // ---- (2) the other owners' codes and scales. One flat index space over (owner, vector):
+  // a thread first issues up to eight peer loads (different owners, all in flight together),
+  // then stores them; a loop of dependent load -> store pairs would be bound by NVLink latency.
   const int vpr = p.h >> 4;  // 16-byte vectors per row of codes
   const int tid = cta * blockDim.x + threadIdx.x;
   const int stride = ctas * blockDim.x;
-  for (int d = 1; d < p.world; ++d) {
-    const int o = (p.rank + d) % p.world;
-    const int ofirst = min(o * rpo, p.m);
-    const int ocount = min(rpo, p.m - ofirst);
-    if (ocount <= 0) continue;
-    const uint8_t* src_codes = p.peers[o] + p.owner_stage_off;
-    const uint8_t* src_scales = src_codes + (size_t)p.m * p.h;
-    uint8_t* dst_codes = p.codes + (size_t)ofirst * p.h;
-    const int total = ocount * vpr;
-    for (int base = tid; base < total; base += 4 * stride) {
-      uint4 v[4];
+  {
+    const int seg = rpo * vpr;
+    const int total = (p.world - 1) * seg;
+    for (int base = tid; base < total; base += 8 * stride) {
+      uint4 v[8];
+      size_t dst[8];
+      bool valid[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         const int idx = base + u * stride;
-        if (idx < total)
-          v[u] = poison ? make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu)
-                        : ld_peer16(src_codes + (size_t)idx * 16);
+        valid[u] = false;
+        if (idx < total) {
+          const int d = idx / seg;
+          const int r = idx - d * seg;
+          const int o = (p.rank + 1 + d) % p.world;
+          const int ofirst = min(o * rpo, p.m);
+          const int ocount = min(rpo, p.m - ofirst);
+          if (r < ocount * vpr) {
+            valid[u] = true;
+            dst[u] = (size_t)ofirst * p.h + (size_t)r * 16;
+            v[u] = poison ? make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu)
+                          : ld_peer16(p.peers[o] + p.owner_stage_off + (size_t)r * 16);
+          }
+        }
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int idx = base + u * stride;
-        if (idx < total) *reinterpret_cast<uint4*>(dst_codes + (size_t)idx * 16) = v[u];
-      }
+      for (int u = 0; u < 8; ++u)
+        if (valid[u]) *reinterpret_cast<uint4*>(p.codes + dst[u]) = v[u];
     }
-    if ((groups & 3) == 0) {
-      const int wpr = groups >> 2;  // 4-byte words per row of scales
-      const int words = ocount * wpr;
-      for (int idx = tid; idx < words; idx += stride) {
-        const int j = idx / wpr, w = idx - j * wpr;
-        const uint32_t s = poison ? 0xFFFFFFFFu : ld_peer4(src_scales + (size_t)idx * 4);
-        *reinterpret_cast<uint32_t*>(p.scales + sf_offset(ofirst + j, w * 4, p.k_tiles)) = s;
+  }
+  const size_t scale_base = p.owner_stage_off + (size_t)p.m * p.h;
+  if ((groups & 3) == 0) {
+    const int wpr = groups >> 2;  // 4-byte words per row of scales
+    const int seg = rpo * wpr;
+    const int total = (p.world - 1) * seg;
+    for (int base = tid; base < total; base += 4 * stride) {
+      uint32_t v[4];
+      size_t dst[4];
+      bool valid[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * stride;
+        valid[u] = false;
+        if (idx < total) {
+          const int d = idx / seg;
+          const int r = idx - d * seg;
+          const int o = (p.rank + 1 + d) % p.world;
+          const int ofirst = min(o * rpo, p.m);
+          const int ocount = min(rpo, p.m - ofirst);
+          if (r < ocount * wpr) {
+            const int j = r / wpr, w = r - j * wpr;
+            valid[u] = true;
+            dst[u] = sf_offset(ofirst + j, w * 4, p.k_tiles);
+            v[u] = poison ? 0xFFFFFFFFu : ld_peer4(p.peers[o] + scale_base + (size_t)r * 4);
+          }
+        }
       }
-    } else {
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (valid[u]) *reinterpret_cast<uint32_t*>(p.scales + dst[u]) = v[u];
+    }
+  } else {
+    for (int d = 1; d < p.world; ++d) {
+      const int o = (p.rank + d) % p.world;
+      const int ofirst = min(o * rpo, p.m);
+      const int ocount = min(rpo, p.m - ofirst);
       const int bytes = ocount * groups;
       for (int idx = tid; idx < bytes; idx += stride) {
         const int j = idx / groups, g = idx - j * groups;
         p.scales[sf_offset(ofirst + j, g, p.k_tiles)] =
-            poison ? (uint8_t)0xFF : (uint8_t)ld_peer1(src_scales + idx);
+            poison ? (uint8_t)0xFF : (uint8_t)ld_peer1(p.peers[o] + scale_base + idx);
       }
     }
   }
@@ -756,13 +791,20 @@ int resident_ctas(int threads, bool local_ranks) {
 int grid_for(const ArParams& p, int threads, int resident) {
   const int per_sm = std::max(1, std::min(4, 2048 / threads));
   int64_t want = std::max<int64_t>(p.m, 1);
-  if (p.owner) want = std::max<int64_t>(p.rows_per_owner, std::min<int64_t>(p.m, 2 * sm_count()));
+  if (p.owner) want = std::max<int64_t>(p.rows_per_owner, 1);
   int ctas = (int)std::min<int64_t>(want, (int64_t)sm_count() * per_sm);
   ctas = std::min(ctas, kMaxCtas);
   if (p.coarse || p.owner) {
     // CTAs wait for flags that a grid's last CTA publishes: all of them must be resident
     ctas = std::min(ctas, resident);
     if (!p.owner) ctas = std::min(ctas, 2 * sm_count());
+  }
+  ctas = std::max(ctas, 1);
+  if (p.owner) {
+    // Every CTA the same number of rows: 512 owned rows on 444 resident CTAs would leave 376
+    // CTAs idle during a second round of 68 rows.
+    const int64_t rounds = (want + ctas - 1) / ctas;
+    ctas = (int)((want + rounds - 1) / rounds);
   }
   return std::max(ctas, 1);
 }

@@ -340,6 +340,102 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict_
   }
 }
 
+// Staged interface (the reference's route / grouped_gemm / silu_grouped_gemm / reduce shims,
+// src/vllm_mach/mxfp6/moe_utils.py:205-488): the activation arrives ALREADY quantised (codes
+// [M, K] + logical scales [M, K/32]). One warp per token copies its row into each of its top-k
+// permuted rows and writes the scale bytes at their swizzled offsets.
+__global__ void __launch_bounds__(256)
+moe_scatter_codes_kernel(const uint8_t* __restrict__ codes_in, const uint8_t* __restrict__ scales_in,
+                         const int* __restrict__ pos_of, int m, int topk,
+                         uint8_t* __restrict__ codes, uint8_t* __restrict__ scales, int k,
+                         int k_tiles) {
+  const int groups = k >> 5;
+  const int vecs = k >> 4;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int warps = (int)((gridDim.x * blockDim.x) >> 5);
+  for (int token = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5); token < m; token += warps) {
+    for (int j = 0; j < topk; ++j) {
+      const int row = pos_of[(size_t)token * topk + j];
+      if (row < 0) continue;  // warp-uniform
+      for (int v = lane; v < vecs; v += 32)
+        *reinterpret_cast<uint4*>(codes + (size_t)row * k + (size_t)v * 16) =
+            __ldg(reinterpret_cast<const uint4*>(codes_in + (size_t)token * k + (size_t)v * 16));
+      for (int g = lane; g < groups; g += 32)
+        scales[sf_offset(row, g, k_tiles)] = __ldg(scales_in + (size_t)token * groups + g);
+    }
+  }
+}
+
+// int64 offsets of the staged interface from the route kernel's int32 outputs:
+// expert_offsets[e] = routed rows of experts < e (true counts), scale_offsets[e] = first row of
+// expert e's 128-row padded segment (the row index space of the permuted activation here).
+__global__ void __launch_bounds__(1024)
+moe_stage_offsets_kernel(const int* __restrict__ counts, const int* __restrict__ offsets,
+                         int experts, long long* __restrict__ expert_offsets,
+                         long long* __restrict__ scale_offsets) {
+  __shared__ int s_warp[32];
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c = tid < experts ? counts[tid] : 0;
+  int r = c;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int o = __shfl_up_sync(0xffffffffu, r, d);
+    if (lane >= d) r += o;
+  }
+  if (lane == 31) s_warp[wid] = r;
+  __syncthreads();
+  int before = 0;
+  for (int j = 0; j < wid; ++j) before += s_warp[j];
+  if (tid < experts) {
+    expert_offsets[tid] = before + r - c;
+    scale_offsets[tid] = offsets[tid];
+  }
+  if (tid == experts - 1) {
+    expert_offsets[experts] = before + r;
+    scale_offsets[experts] = offsets[experts];
+  }
+}
+
+// Work list (expert, first row, rows <= chunk_rows) from the staged interface's offsets.
+__global__ void __launch_bounds__(1024)
+moe_work_from_offsets_kernel(const long long* __restrict__ expert_offsets,
+                             const long long* __restrict__ scale_offsets, int experts,
+                             int chunk_rows, int max_work, int* __restrict__ work,
+                             int* __restrict__ num_work) {
+  __shared__ int s_warp[32];
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c = tid < experts ? (int)(expert_offsets[tid + 1] - expert_offsets[tid]) : 0;
+  const int items = (c + chunk_rows - 1) / chunk_rows;
+  int w = items;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int o = __shfl_up_sync(0xffffffffu, w, d);
+    if (lane >= d) w += o;
+  }
+  if (lane == 31) s_warp[wid] = w;
+  __syncthreads();
+  int before = 0;
+  for (int j = 0; j < wid; ++j) before += s_warp[j];
+  int nw = before + w - items;
+  if (tid < experts) {
+    const int first = (int)scale_offsets[tid];
+    for (int r = 0; r < c; r += chunk_rows, ++nw) {
+      if (nw < max_work) {
+        work[3 * nw] = tid;
+        work[3 * nw + 1] = first + r;
+        work[3 * nw + 2] = min(chunk_rows, c - r);
+      }
+    }
+  }
+  if (tid == experts - 1) *num_work = min(before + w, max_work);
+}
+
 }  // namespace
 }  // namespace mach
 
@@ -459,4 +555,51 @@ extern "C" int mach_moe_combine(const void* y_bf16, const void* topk_weights_f32
                             (const __nv_bfloat16*)y_bf16, (const float*)topk_weights_f32,
                             (const int*)pos_of, (__nv_bfloat16*)out_bf16, (int)m, (int)h, (int)topk),
                   "moe_combine");
+}
+
+extern "C" int mach_moe_scatter_codes(const void* codes_in, const void* logical_scales,
+                                      const void* pos_of, int64_t m, int64_t topk, int64_t k,
+                                      void* codes, void* scales, void* stream) {
+  if (!codes_in || !logical_scales || !pos_of || !codes || !scales)
+    return fail(MACH_ERR_INVALID, "moe_scatter_codes: null pointer");
+  if (k % 32 || k <= 0 || m < 0 || topk < 1 || !aligned16(codes_in) || !aligned16(codes))
+    return fail(MACH_ERR_UNSUPPORTED, "moe_scatter_codes: K %% 32 and 16-byte alignment");
+  if (m == 0) return MACH_OK;
+  const int blocks = (int)std::max<int64_t>(1, std::min<int64_t>((m + 7) / 8, (int64_t)sm_count() * 8));
+  return launched(launch_ex(moe_scatter_codes_kernel, dim3((unsigned)blocks), dim3(256), 0,
+                            (cudaStream_t)stream, dim3(1, 1, 1), pdl_enabled(),
+                            (const uint8_t*)codes_in, (const uint8_t*)logical_scales,
+                            (const int*)pos_of, (int)m, (int)topk, (uint8_t*)codes,
+                            (uint8_t*)scales, (int)k, (int)((k + 127) / 128)),
+                  "moe_scatter_codes");
+}
+
+extern "C" int mach_moe_stage_offsets(const void* counts, const void* offsets, int64_t experts,
+                                      void* expert_offsets_i64, void* scale_offsets_i64,
+                                      void* stream) {
+  if (!counts || !offsets || !expert_offsets_i64 || !scale_offsets_i64)
+    return fail(MACH_ERR_INVALID, "moe_stage_offsets: null pointer");
+  if (experts < 1 || experts > kMaxExperts)
+    return fail(MACH_ERR_UNSUPPORTED, "moe_stage_offsets: 1 <= experts <= 1024");
+  return launched(launch_ex(moe_stage_offsets_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream,
+                            dim3(1, 1, 1), pdl_enabled(), (const int*)counts, (const int*)offsets,
+                            (int)experts, (long long*)expert_offsets_i64,
+                            (long long*)scale_offsets_i64),
+                  "moe_stage_offsets");
+}
+
+extern "C" int mach_moe_work_from_offsets(const void* expert_offsets_i64,
+                                          const void* scale_offsets_i64, int64_t experts,
+                                          int64_t chunk_rows, int64_t work_cap, void* work,
+                                          void* num_work, void* stream) {
+  if (!expert_offsets_i64 || !scale_offsets_i64 || !work || !num_work)
+    return fail(MACH_ERR_INVALID, "moe_work_from_offsets: null pointer");
+  if (experts < 1 || experts > kMaxExperts || chunk_rows < 1 || work_cap < 1)
+    return fail(MACH_ERR_UNSUPPORTED, "moe_work_from_offsets: bad sizes");
+  return launched(launch_ex(moe_work_from_offsets_kernel, dim3(1), dim3(1024), 0,
+                            (cudaStream_t)stream, dim3(1, 1, 1), pdl_enabled(),
+                            (const long long*)expert_offsets_i64,
+                            (const long long*)scale_offsets_i64, (int)experts, (int)chunk_rows,
+                            (int)work_cap, (int*)work, (int*)num_work),
+                  "moe_work_from_offsets");
 }

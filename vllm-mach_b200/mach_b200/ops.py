@@ -3,7 +3,10 @@ on libmach_b200.so. Every op has a fake (meta) implementation that keeps the bat
 symbolic, so the ops trace under torch.compile(fullgraph=True, dynamic=True) exactly like
 the reference's (src/vllm_mach/mxfp6/dense_mxfp8.py:100-110, mxfp6/dense.py:132-156,
 mxfp6/mxfp8_mlp.py:25-30, mxfp6/mxfp8_norm_quant.py:75-80, mxfp6/gemma_norm.py:48-55,
-mxfp6/compiled_ar_norm.py:7-13, fp8/linear.py:84-97, fp8/activation.py:23-27).
+mxfp6/compiled_ar_norm.py:7-13, fp8/linear.py:84-97, fp8/activation.py:23-27), the ops the
+reference's native extensions define (native/ar_norm/binding.cu:72-80,
+native/block_fp8/block_fp8.cu:257-262, native/fp8_activation/activation.cu:98-104) and the
+mixture-of-experts shims of src/vllm_mach/mxfp6/moe_utils.py:47-488.
 
 The op names keep the reference's spelling (including "sm120") so that adapters and compiled
 graphs that name them keep working; the implementation is sm_100a.
@@ -28,11 +31,29 @@ def _mxfp8_gemm(x, weight, weight_scale):
     return native.mx_gemm(codes, scales, weight.view(torch.uint8), weight_scale, "e4m3")
 
 
-def _mxfp6_gemm(x, weight, weight_scale, n: int, dtype, fmt: str = "e3m2"):
+# 6-bit element format of the checkpoint's MXFP6 weights. The reference admits E3M2 only
+# (src/vllm_mach/mxfp6/dense.py:172-177) and its op schemas carry no format argument, so the
+# format is process state set at load time (`set_mxfp6_format`, called by
+# Mxfp6B200LinearKernel.process_weights_after_loading from the layer's quantisation config).
+_mxfp6_format = "e3m2"
+
+
+def set_mxfp6_format(fmt: str) -> None:
+    global _mxfp6_format
+    if fmt not in ("e3m2", "e2m3"):
+        raise ValueError(f"unknown MXFP6 element format {fmt!r}")
+    _mxfp6_format = fmt
+
+
+def current_mxfp6_format() -> str:
+    return _mxfp6_format
+
+
+def _mxfp6_gemm(x, weight, weight_scale, n: int, dtype):
     if dtype != torch.bfloat16:
         raise ValueError("the B200 W6A8 GEMM returns BF16")
     codes, scales = native.quantize_mxfp8(x)
-    out = native.mx_gemm(codes, scales, weight, weight_scale, fmt)
+    out = native.mx_gemm(codes, scales, weight, weight_scale, current_mxfp6_format())
     if out.shape[1] != n:
         raise ValueError(f"weight has {out.shape[1]} rows, expected N={n}")
     return out
@@ -81,9 +102,132 @@ def _silu_and_mul_per_block_quant(out, input, scales, group_size: int, scale_ub,
                                   is_scale_transposed: bool):
     if group_size != 128 or scale_ub is not None:
         raise ValueError("the B200 SiLU/FP8 producer implements group 128 without an upper bound")
-    q, s = native.silu_mul_fp8_group_quantize(input, transposed=is_scale_transposed)
-    out.copy_(q.view(out.dtype))
-    scales.copy_(s)
+    _fp8_activation_run(out, input, scales, is_scale_transposed)
+
+
+def _fp8_activation_run(out, input, scales, is_scale_transposed: bool):
+    """mach_fp8_activation::run: writes straight into the caller's `out` and `scales`."""
+    rows, two_i = input.shape
+    inter = two_i // 2
+    if (input.dtype != torch.bfloat16 or out.dtype != torch.float8_e4m3fn
+            or scales.dtype != torch.float32):
+        raise RuntimeError("Expected BF16, E4M3, FP32 tensors")
+    if tuple(out.shape) != (rows, inter) or tuple(scales.shape) != (rows, inter // 128):
+        raise RuntimeError("out must be [M, I] and scales [M, I/128]")
+    if not input.is_contiguous() or not out.is_contiguous():
+        raise RuntimeError("input and out must be contiguous")
+    ok = (scales.stride() == (1, rows) or rows == 1) if is_scale_transposed else scales.is_contiguous()
+    if not ok:
+        raise RuntimeError("Unexpected scale layout")
+    native.silu_mul_fp8_group_quantize(input, transposed=is_scale_transposed, out=out,
+                                       scales=scales)
+
+
+def _block_fp8_mm(a, b, sa, sb):
+    """vllm_mach_block_fp8::mm: `b` is the weight viewed [K, N] (column-major, i.e. the
+    checkpoint's [N, K] transposed) and `sb` its scales viewed [K/128, N/128] or, as the
+    reference's 64-row variant passes them, [K/128, N/64] with every value repeated."""
+    if b.ndim != 2 or b.stride(0) != 1:
+        raise RuntimeError("b must be the column-major [K, N] view of an [N, K] weight")
+    weight = b.t()
+    k = a.shape[1]
+    n = weight.shape[0]
+    scale = sb.t()
+    if scale.shape[0] == (n + 63) // 64 and scale.shape[0] != (n + 127) // 128:
+        scale = scale[::2]
+    return native.block_fp8_gemm(a, sa, weight, scale.contiguous())
+
+
+_NORM_QUANT_ABI = "ar-norm-mxfp8-b200-v1"
+
+
+def _norm_quant_run(hidden, residual, gamma, workspace, norm, residual_out, quant, scales,
+                    rank: int, eps: float, fused: bool):
+    """mach_norm_quant::run on the B200 reduce. `workspace` is the int64 tensor
+    `collective.workspace_tensor` returns (the reference passes FlashInfer's pointer table in
+    the same argument). `residual_out` may alias `hidden`, as the reference's caller does
+    (src/vllm_mach/mxfp6/ar_norm.py:136-140)."""
+    from . import collective
+    m, h = hidden.shape
+    for t in (hidden, residual, gamma, norm, residual_out):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.device != hidden.device:
+            raise RuntimeError("mach_norm_quant.run BF16 tensors must be contiguous and on "
+                               "hidden's device")
+    if residual.shape != hidden.shape or norm.shape != hidden.shape \
+            or residual_out.shape != hidden.shape or gamma.numel() != h:
+        raise RuntimeError("mach_norm_quant.run requires residual, norm and residual_out to "
+                           "match hidden and gamma.numel() == hidden size")
+    ws = collective.workspace_from_tensor(workspace)
+    if ws.rank != rank:
+        raise RuntimeError(f"mach_norm_quant.run: workspace belongs to rank {ws.rank}, not {rank}")
+    if fused:
+        if quant.dtype not in (torch.uint8, torch.float8_e4m3fn) or quant.shape != hidden.shape \
+                or not quant.is_contiguous():
+            raise RuntimeError("mach_norm_quant.run requires a contiguous one-byte quant tensor "
+                               "matching hidden")
+        if scales.dtype != torch.uint8 or scales.numel() < native.sf_bytes(m, h):
+            raise RuntimeError("mach_norm_quant.run requires a uint8 scale tensor with "
+                               f"{native.sf_bytes(m, h)} entries")
+    if m == 0:
+        return
+    with torch.cuda.device(hidden.device):
+        native._check(native.lib().mach_allreduce_residual_rmsnorm_mxfp8(
+            ws.handle, native._ptr(hidden), native._ptr(residual), native._ptr(gamma), eps, 1.0,
+            native._ptr(norm), native._ptr(residual_out),
+            native._ptr(quant) if fused else None, native._ptr(scales) if fused else None,
+            m, h, 0, native._stream(hidden)), "mach_norm_quant.run")
+
+
+# ---- mixture-of-experts shims (src/vllm_mach/mxfp6/moe_utils.py:47-488)
+def _moe_quantize_mxfp8(input):
+    codes, scales = native.quantize_mxfp8(input)
+    return codes, native.unpack_scales(scales, input.shape[0], input.shape[1])
+
+
+def _moe_quantize_mxfp8_packed(input):
+    return native.quantize_mxfp8(input)
+
+
+def _moe_reduce(output, routed_output, topk_weights, inverse_permutation):
+    from . import moe
+    moe.combine(routed_output, topk_weights, inverse_permutation, output)
+
+
+def _moe_whole_layer(output, hidden_states, w1, w1_scale, w2, w2_scale, topk_weights, topk_ids,
+                     workspace13, workspace2):
+    from . import moe
+    weights = moe.cached_weights(w1, w1_scale, w2, w2_scale)
+    moe.experts_forward(hidden_states, weights, topk_weights, topk_ids, out=output)
+
+
+def _moe_route(permuted_activation, activation, logical_scales, topk_ids, expert_map,
+               local_experts: int):
+    from . import moe
+    return moe.route_quantized(permuted_activation, activation, logical_scales, topk_ids,
+                               expert_map, local_experts)
+
+
+def _moe_grouped_gemm(output, activation, packed_scales, weight, weight_scales, expert_offsets,
+                      scale_offsets):
+    from . import moe
+    moe.grouped_gemm_stage(output, activation, packed_scales, weight, weight_scales,
+                           expert_offsets, swiglu_input=None)
+
+
+def _moe_silu_grouped_gemm(output, gate_up, weight, weight_scales, expert_offsets, scale_offsets):
+    from . import moe
+    moe.grouped_gemm_stage(output, None, None, weight, weight_scales, expert_offsets,
+                           swiglu_input=gate_up)
+
+
+def _moe_route_fake(permuted_activation, activation, logical_scales, topk_ids, expert_map,
+                    local_experts: int):
+    routes = activation.shape[0] * topk_ids.shape[1]
+    scale_rows = routes + local_experts * 127
+    dev = activation.device
+    offsets = torch.empty(local_experts + 1, dtype=torch.int64, device=dev)
+    return (torch.empty(scale_rows * (activation.shape[1] // 32), dtype=torch.uint8, device=dev),
+            offsets, torch.empty_like(offsets), torch.empty(routes, dtype=torch.int32, device=dev))
 
 
 def _empty_rows(x, n):
@@ -99,7 +243,8 @@ _SCHEMAS = [
     ("vllm", "mach_swiglu_mxfp8_down(Tensor gate_up, Tensor weight, Tensor weight_scale) -> Tensor",
      lambda g, w, s: _swiglu_down(g, w, s, "e4m3"), lambda g, w, s: _empty_rows(g, w.shape[0])),
     ("vllm", "mach_swiglu_mxfp6_down(Tensor gate_up, Tensor weight, Tensor weight_scale) -> Tensor",
-     lambda g, w, s: _swiglu_down(g, w, s, "e3m2"), lambda g, w, s: _empty_rows(g, w.shape[0])),
+     lambda g, w, s: _swiglu_down(g, w, s, current_mxfp6_format()),
+     lambda g, w, s: _empty_rows(g, w.shape[0])),
     ("vllm", "mach_norm_quant_mxfp8_gate_up(Tensor x, Tensor residual, Tensor norm_weight, "
              "float eps, Tensor weight, Tensor weight_scale) -> (Tensor, Tensor)",
      _norm_quant_gate_up,
@@ -122,11 +267,53 @@ _SCHEMAS = [
     ("vllm_mach_fp8", "silu_and_mul_per_block_quant(Tensor(a!) out, Tensor input, Tensor(b!) scales, "
                       "int group_size, Tensor? scale_ub, bool is_scale_transposed) -> ()",
      _silu_and_mul_per_block_quant, lambda *a: None),
+    ("mach_fp8_activation", "run(Tensor(a!) out, Tensor input, Tensor(b!) scales, "
+                            "bool is_scale_transposed) -> ()",
+     _fp8_activation_run, lambda *a: None),
+    ("vllm_mach_block_fp8", "mm(Tensor a, Tensor b, Tensor sa, Tensor sb) -> Tensor",
+     _block_fp8_mm, lambda a, b, sa, sb: a.new_empty((a.shape[0], b.shape[1]),
+                                                     dtype=torch.bfloat16)),
+    ("mach_norm_quant", "run(Tensor hidden, Tensor residual, Tensor gamma, Tensor workspace, "
+                        "Tensor(a!) norm, Tensor(b!) residual_out, Tensor(c!) quant, "
+                        "Tensor(d!) scales, int rank, float eps, bool fused) -> ()",
+     _norm_quant_run, lambda *a: None),
+    ("vllm", "mxfp6_sm120_quantize_mxfp8(Tensor input) -> (Tensor, Tensor)",
+     _moe_quantize_mxfp8,
+     lambda x: (torch.empty_like(x, dtype=torch.float8_e4m3fn),
+                torch.empty((x.shape[0], x.shape[1] // 32), dtype=torch.uint8, device=x.device))),
+    ("vllm", "mxfp6_sm120_quantize_mxfp8_packed(Tensor input) -> (Tensor, Tensor)",
+     _moe_quantize_mxfp8_packed,
+     lambda x: (torch.empty_like(x, dtype=torch.float8_e4m3fn),
+                torch.empty(((x.shape[0] + 127) // 128 * 128 * ((x.shape[1] + 127) // 128) * 4,),
+                            dtype=torch.uint8, device=x.device))),
+    ("vllm", "mxfp6_sm120_route(Tensor(a!) permuted_activation, Tensor activation, "
+             "Tensor logical_scales, Tensor topk_ids, Tensor? expert_map, int local_experts) "
+             "-> (Tensor, Tensor, Tensor, Tensor)",
+     _moe_route, _moe_route_fake),
+    ("vllm", "mxfp6_sm120_grouped_gemm(Tensor(a!) output, Tensor activation, Tensor packed_scales, "
+             "Tensor weight, Tensor weight_scales, Tensor expert_offsets, Tensor scale_offsets) -> ()",
+     _moe_grouped_gemm, lambda *a: None),
+    ("vllm", "mxfp6_sm120_silu_grouped_gemm(Tensor(a!) output, Tensor gate_up, Tensor weight, "
+             "Tensor weight_scales, Tensor expert_offsets, Tensor scale_offsets) -> ()",
+     _moe_silu_grouped_gemm, lambda *a: None),
+    ("vllm", "mxfp6_sm120_reduce(Tensor(a!) output, Tensor routed_output, Tensor topk_weights, "
+             "Tensor inverse_permutation) -> ()",
+     _moe_reduce, lambda *a: None),
+    ("vllm", "mxfp6_sm120_qwen35_grouped_moe(Tensor(a!) output, Tensor hidden_states, Tensor w1, "
+             "Tensor w1_scale, Tensor w2, Tensor w2_scale, Tensor topk_weights, Tensor topk_ids, "
+             "Tensor(b!) workspace13, Tensor(c!) workspace2) -> ()",
+     _moe_whole_layer, lambda *a: None),
+]
+
+_DEFS_ONLY = [
+    # (namespace, schema, python implementation registered for every backend)
+    ("mach_norm_quant", "abi() -> str", lambda: _NORM_QUANT_ABI),
 ]
 
 
 def op_names() -> list[str]:
-    return [f"{ns}::{schema.split('(')[0]}" for ns, schema, _, _ in _SCHEMAS]
+    return ([f"{ns}::{schema.split('(')[0]}" for ns, schema, _, _ in _SCHEMAS]
+            + [f"{ns}::{schema.split('(')[0]}" for ns, schema, _ in _DEFS_ONLY])
 
 
 def register() -> None:
@@ -143,5 +330,13 @@ def register() -> None:
             lib.define(schema)
             lib.impl(name, impl, "CUDA")
             torch.library.register_fake(f"{ns}::{name}", fake, lib=lib)
+            _libs.append(lib)
+        for ns, schema, impl in _DEFS_ONLY:
+            name = schema.split("(")[0]
+            if hasattr(getattr(torch.ops, ns), name):
+                continue
+            lib = torch.library.Library(ns, "FRAGMENT")
+            lib.define(schema)
+            lib.impl(name, impl, "CompositeExplicitAutograd")
             _libs.append(lib)
         _registered = True
