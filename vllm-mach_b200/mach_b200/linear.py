@@ -59,6 +59,17 @@ class Mxfp8B200LinearKernel(_Mxfp8Base):
 
     @classmethod
     def can_implement(cls, config):
+        """MXFP8 weights (E4M3 + E8M0 per 32) with dynamic MXFP8 activations and BF16 output;
+        a config that names other formats is refused with a reason."""
+        wq = str(getattr(config, "weight_quant_key", "") or "").lower()
+        aq = str(getattr(config, "activation_quant_key", "") or "").lower()
+        out = getattr(config, "out_dtype", None)
+        if wq and "mxfp8" not in wq and "e4m3" not in wq:
+            return False, "requires static MXFP8 E4M3 weights"
+        if aq and "mxfp8" not in aq and "e4m3" not in aq:
+            return False, "requires dynamic MXFP8 E4M3 activations"
+        if out is not None and out != torch.bfloat16:
+            return False, "requires BF16 output"
         return True, None
 
     def process_weights_after_loading(self, layer):
@@ -101,6 +112,19 @@ def logical_weight_shape(weight: torch.Tensor) -> tuple[int, int]:
     return n, k
 
 
+def mxfp6_format_of(layer, default: str = "e3m2") -> str:
+    """6-bit element format of a layer's weights from its quantisation config: the reference
+    admits "fp6_e3m2" only (src/vllm_mach/mxfp6/dense.py:172-177); B200 also takes "fp6_e2m3"."""
+    for holder in (layer, getattr(layer, "scheme", None), getattr(layer, "quant_config", None)):
+        for attr in ("weight_dtype", "weight_quant_key", "ocp_mx_scheme", "weight_format"):
+            text = str(getattr(holder, attr, "") or "").lower()
+            if "e2m3" in text:
+                return "e2m3"
+            if "e3m2" in text:
+                return "e3m2"
+    return default
+
+
 class Mxfp6B200LinearKernel(_Mxfp6Base):
     """W6A8: static MXFP6 weights (E3M2 as the reference admits, or E2M3), dynamic MXFP8
     activations."""
@@ -125,6 +149,9 @@ class Mxfp6B200LinearKernel(_Mxfp6Base):
         n, k = logical_weight_shape(layer.weight)
         if n % 16:
             raise ValueError("the B200 W6A8 GEMM requires N % 16 == 0")
+        fmt = mxfp6_format_of(layer, self.weight_format)
+        ops.set_mxfp6_format(fmt)
+        self.weight_format = fmt
         scale = layer.weight_scale.data
         if scale.dtype != torch.uint8 or tuple(scale.shape) != (n, k // 32):
             raise ValueError("MXFP6 requires uint8 E8M0 scales shaped [N, K/32]")

@@ -196,7 +196,7 @@ def _moe_reduce(output, routed_output, topk_weights, inverse_permutation):
 def _moe_whole_layer(output, hidden_states, w1, w1_scale, w2, w2_scale, topk_weights, topk_ids,
                      workspace13, workspace2):
     from . import moe
-    weights = moe.cached_weights(w1, w1_scale, w2, w2_scale)
+    weights = moe.cached_weights(w1, w1_scale, w2, w2_scale, current_mxfp6_format())
     moe.experts_forward(hidden_states, weights, topk_weights, topk_ids, out=output)
 
 
@@ -211,13 +211,13 @@ def _moe_grouped_gemm(output, activation, packed_scales, weight, weight_scales, 
                       scale_offsets):
     from . import moe
     moe.grouped_gemm_stage(output, activation, packed_scales, weight, weight_scales,
-                           expert_offsets, swiglu_input=None)
+                           expert_offsets, scale_offsets, fmt=current_mxfp6_format())
 
 
 def _moe_silu_grouped_gemm(output, gate_up, weight, weight_scales, expert_offsets, scale_offsets):
     from . import moe
     moe.grouped_gemm_stage(output, None, None, weight, weight_scales, expert_offsets,
-                           swiglu_input=gate_up)
+                           scale_offsets, swiglu_input=gate_up, fmt=current_mxfp6_format())
 
 
 def _moe_route_fake(permuted_activation, activation, logical_scales, topk_ids, expert_map,
