@@ -75,6 +75,15 @@ MACH_API int mach_mxfp8_quantize(const void* x_bf16, int64_t ldx, void* codes, v
 MACH_API int mach_swiglu_mxfp8_quantize(const void* gate_up_bf16, void* codes, void* scales, int64_t m,
                                int64_t i, void* stream);
 
+/* The same producer with the reference's OTHER SwiGLU contract ("champion", for its MXFP8
+ * 4B/2B profile, src/vllm_mach/mxfp8/swiglu_quant.py:46-70; the two must not be mixed up):
+ * v = bf16(silu(gate) * up) with ONE BF16 rounding; E8M0 = smallest power of two >=
+ * amax * rcp.approx(448) (cvt.rp.satfinite.ue8m0x2); codes = e4m3(clamp(v * rcp.approx(2^e)));
+ * an all-zero block stores scale byte 0 and zero codes. */
+MACH_API int mach_swiglu_mxfp8_quantize_champion(const void* gate_up_bf16, void* codes,
+                                                 void* scales, int64_t m, int64_t i,
+                                                 void* stream);
+
 /* s = x + residual (FP32); residual_out = bf16(s);
  * y = bf16(s * rsqrt(mean(s^2) + eps) * (weight + weight_bias)); then MXFP8 of y.
  * Replaces _norm / _norm_quant (src/vllm_mach/mxfp6/gemma_norm.py:13-29,
@@ -96,6 +105,14 @@ MACH_API int mach_residual_rmsnorm_rounded_mxfp8(const void* a_bf16, const void*
                                                  float weight_bias, void* norm_out_bf16,
                                                  void* residual_out_bf16, void* codes,
                                                  void* scales, int64_t m, int64_t h, void* stream);
+
+/* Checkpoint weight quantiser: BF16 [N, K] -> E4M3 codes [N, K] + LOGICAL E8M0 scales uint8
+ * [N, K/32], by the rule of quantize_block (src/vllm_mach/mxfp8/reconstruct_model.py:34-50;
+ * golden vector tests/test_mxfp8_reconstruct_model.py:142-156): maximum m of the block in BF16,
+ * mantissa rounded up from 0.75 ((bits + 32) & 0xFF80), E8M0 = 127 + floor(log2) - 8, codes =
+ * RTNE(x / 2^(E8M0 - 127)). A load-time / conversion-time step. K % 32 == 0. */
+MACH_API int mach_mxfp8_quantize_weight(const void* w_bf16, void* codes, void* logical_scales,
+                                        int64_t n, int64_t k, void* stream);
 
 /* uint8 [rows, K/32] logical <-> swizzled. Pad bytes of the swizzled buffer are written as
  * 127 (scale 1.0) by pack. Replaces mxfp6.pack_scales / unpack_scales

@@ -155,6 +155,41 @@ def swiglu_quantize(gate_up: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return quantize_mxfp8(swiglu_values(gate_up))
 
 
+def swiglu_quantize_champion(gate_up: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """The "champion" SwiGLU producer: BF16 [M, 2I] -> (E4M3 codes [M, I], E8M0 [M, I/32]).
+
+    src/vllm_mach/mxfp8/swiglu_quant.py:46-70: values = bf16((gate / (1 + exp(-gate))) * up)
+    with ONE BF16 rounding; raw = amax * rcp(448); scale byte = cvt.rp.satfinite.ue8m0 of raw
+    (smallest power of two >= raw; 0 for raw == 0); inverse = rcp(2^(e-127)), 0 when e == 0;
+    codes = e4m3(clamp(values * inverse, +-448)).
+    PARITY UNPINNED: the reference states this kernel with inline PTX (rcp.approx.ftz,
+    cvt.rp...ue8m0x2) that the Triton interpreter rejects, and its only test compares with
+    FlashInfer on an SM120 GPU (tests/test_mxfp8_swiglu_quant.py:89-109). Taken here: exp
+    correctly rounded, IEEE division, rcp.approx(448) = the FP32 nearest 1/448 and exact
+    reciprocals of powers of two."""
+    m, two_i = gate_up.shape
+    inter = two_i // 2
+    g = gate_up[:, :inter].float()
+    u = gate_up[:, inter:].float()
+    values = bf16((g / (1.0 + exp_cr(-g))) * u)
+    v = values.reshape(m, inter // 32, 32)
+    amax = v.abs().amax(-1)
+    raw = amax * torch.tensor(1.0 / 448.0, dtype=torch.float32)
+    bits = _f32_bits(raw)
+    exponent = (bits >> 23) & 0xFF
+    mantissa = bits & 0x7FFFFF
+    byte = exponent + (mantissa != 0).to(torch.int32)
+    # subnormal raw: (2^-127, 2^-126) -> 2^-126 (byte 1); (0, 2^-127] -> 2^-127 (byte 0)
+    sub = exponent == 0
+    byte = torch.where(sub, (mantissa > 0x400000).to(torch.int32), byte)
+    byte = torch.clamp(byte, 0, 254)
+    inverse = torch.where(byte > 0, torch.exp2(127.0 - byte.float()), torch.zeros_like(raw))
+    inverse = torch.where(byte >= 254, torch.zeros_like(raw), inverse)   # 2^-127 flushes to zero
+    q = torch.clamp(v * inverse[..., None], -E4M3_MAX, E4M3_MAX)
+    codes = q.to(torch.float8_e4m3fn).view(torch.uint8).reshape(m, inter)
+    return codes, byte.to(torch.uint8)
+
+
 # --------------------------------------------------------------------------- norms
 def gemma_rmsnorm(x, residual, weight, eps: float, weight_bias: float = 1.0):
     """Residual + RMSNorm on the UNROUNDED sum.

@@ -110,3 +110,25 @@ def test_silu_mul_fp8_group_quantize_bit_exact(nat, m, inter, transposed):
     ref_q, ref_s = ora.silu_mul_fp8_group_quantize(inp)
     assert bytes_equal(s.contiguous(), ref_s), mismatch_report(s.contiguous(), ref_s)
     assert bytes_equal(q, ref_q), mismatch_report(q, ref_q)
+
+
+@pytest.mark.parametrize("m,inter", [(1, 64), (16, 9216), (33, 6144), (513, 256)])
+def test_champion_swiglu_contract(nat, m, inter):
+    """mach_swiglu_mxfp8_quantize_champion vs the oracle's restatement of
+    src/vllm_mach/mxfp8/swiglu_quant.py:46-70 (parity unpinned: see the oracle), over the
+    magnitudes of tests/test_mxfp8_swiglu_quant.py:103, bit for bit."""
+    import ctypes
+    lib = nat.lib()
+    base = randn_bf16(m, 2 * inter, 600 + m).float()
+    for magnitude in (1.0, 0.0, 1.0e-15, 50.0):
+        x = (base * magnitude).to(torch.bfloat16)
+        dev = x.cuda()
+        codes = torch.empty((m, inter), dtype=torch.uint8, device="cuda")
+        scales = torch.zeros(nat.sf_bytes(m, inter), dtype=torch.uint8, device="cuda")
+        nat._check(lib.mach_swiglu_mxfp8_quantize_champion(
+            dev.data_ptr(), codes.data_ptr(), scales.data_ptr(), m, inter,
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "champion")
+        torch.cuda.synchronize()
+        ref_codes, ref_scales = ora.swiglu_quantize_champion(x)
+        assert torch.equal(ora.unswizzle_scales(scales.cpu(), m, inter), ref_scales), magnitude
+        assert torch.equal(codes.cpu(), ref_codes), magnitude

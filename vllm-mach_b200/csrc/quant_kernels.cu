@@ -38,7 +38,10 @@ __device__ __forceinline__ uint2 quantize8(const float (&f)[8], float inv) {
 }
 
 // One unit = one (row, 32-K block); four threads per unit, eight values per thread.
-template <bool kSwiglu>
+// kMode: 0 plain BF16 input; 1 SwiGLU with the rounding points of
+// src/vllm_mach/mxfp6/mxfp8_mlp.py:87-110; 2 SwiGLU with the champion contract of
+// src/vllm_mach/mxfp8/swiglu_quant.py:46-70.
+template <int kMode>
 __global__ void __launch_bounds__(256)
 mx_quantize_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, uint8_t* __restrict__ codes,
                    uint8_t* __restrict__ scales, int64_t m, int k, int k_tiles) {
@@ -66,29 +69,75 @@ mx_quantize_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, uint8_t* __
       if (valid[u]) {
         const __nv_bfloat16* src = x + row[u] * ldx + g[u] * 32 + sub * 8;
         raw[u] = __ldg(reinterpret_cast<const uint4*>(src));
-        if (kSwiglu) raw_up[u] = __ldg(reinterpret_cast<const uint4*>(src + k));
+        if (kMode != 0) raw_up[u] = __ldg(reinterpret_cast<const uint4*>(src + k));
       }
     }
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       float f[8];
-      if (kSwiglu) {
+      if (kMode != 0) {
         float gate[8], up[8];
         unpack_bf16x8(raw[u], gate);
         unpack_bf16x8(raw_up[u], up);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = swiglu_bf16(gate[i], up[i]);
+        for (int i = 0; i < 8; ++i)
+          f[i] = kMode == 1 ? swiglu_bf16(gate[i], up[i]) : swiglu_once_bf16(gate[i], up[i]);
       } else {
         unpack_bf16x8(raw[u], f);
       }
       const float amax = amax8_quad(f);
-      const uint32_t bits = mx_scale_bits(amax);
-      const float inv = mx_inverse(bits);
+      uint32_t scale_byte;
+      float inv;
+      if (kMode == 2) {
+        scale_byte = ue8m0_round_up(__fmul_rn(amax, rcp_approx_ftz(448.0f)));
+        inv = scale_byte > 0 ? rcp_approx_ftz(__uint_as_float(scale_byte << 23)) : 0.0f;
+      } else {
+        const uint32_t bits = mx_scale_bits(amax);
+        inv = mx_inverse(bits);
+        scale_byte = bits >> 23;
+      }
       if (valid[u]) {
         *reinterpret_cast<uint2*>(codes + row[u] * k + g[u] * 32 + sub * 8) = quantize8(f, inv);
-        if (sub == 0) scales[sf_offset((int)row[u], g[u], k_tiles)] = (uint8_t)(bits >> 23);
+        if (sub == 0) scales[sf_offset((int)row[u], g[u], k_tiles)] = (uint8_t)scale_byte;
       }
     }
+  }
+}
+
+
+// Checkpoint weight quantiser (src/vllm_mach/mxfp8/reconstruct_model.py:34-50): per row and 32 K,
+// BF16 maximum m; rounded = bf16 bits (m + 32) & 0xFF80 (the mantissa rounded up from 0.75);
+// E8M0 = 127 + floor(log2(rounded)) - 8 = exponent field of `rounded` - 8; codes =
+// RTNE e4m3(x / 2^(E8M0 - 127)). Logical (row-major) scales out, as checkpoints store them.
+// A zero block gives scale 0 and zero codes. Blocks whose maximum is below 2^-119 would need a
+// negative exponent byte, which the reference leaves to an out-of-range float -> uint8
+// conversion; here the byte is clamped to 0.
+__global__ void __launch_bounds__(256)
+mx_quantize_weight_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ codes,
+                          uint8_t* __restrict__ scales, int64_t n, int k) {
+  const int groups = k >> 5;
+  const int64_t units = n * groups;
+  const int sub = threadIdx.x & 3;
+  for (int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 2) + (threadIdx.x >> 2); unit < units;
+       unit += (int64_t)gridDim.x * (blockDim.x >> 2)) {
+    const int64_t row = unit / groups;
+    const int g = (int)(unit - row * groups);
+    float f[8];
+    unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(x + row * k + g * 32 + sub * 8)), f);
+    const float amax = amax8_quad(f);
+    const uint32_t bits = __float_as_uint(amax) >> 16;         // BF16 bit pattern (amax >= 0)
+    const uint32_t rounded = (bits + 32u) & 0xFF80u;
+    const int exponent = (int)(rounded >> 7);                  // biased exponent field
+    const int byte = exponent > 8 ? exponent - 8 : 0;
+    // x / 2^(byte - 127): division by a power of two, exact unless the quotient is subnormal
+    const float scale = byte > 0 ? __uint_as_float((uint32_t)byte << 23) : 5.877471754111438e-39f;
+    uint2 q;
+    q.x = e4m3x4(__fdiv_rn(f[0], scale), __fdiv_rn(f[1], scale), __fdiv_rn(f[2], scale),
+                 __fdiv_rn(f[3], scale));
+    q.y = e4m3x4(__fdiv_rn(f[4], scale), __fdiv_rn(f[5], scale), __fdiv_rn(f[6], scale),
+                 __fdiv_rn(f[7], scale));
+    *reinterpret_cast<uint2*>(codes + row * k + g * 32 + sub * 8) = q;
+    if (sub == 0) scales[row * groups + g] = (uint8_t)byte;
   }
 }
 
@@ -393,7 +442,7 @@ extern "C" int mach_mxfp8_quantize(const void* x, int64_t ldx, void* codes, void
     return fail(MACH_ERR_UNSUPPORTED, "mxfp8_quantize: K %% 32, ldx %% 8 and 16-byte alignment required");
   if (m > INT32_MAX || k > INT32_MAX) return fail(MACH_ERR_UNSUPPORTED, "mxfp8_quantize: size");
   const int64_t units = m * (k / 32);
-  const cudaError_t e = launch_ex(mx_quantize_kernel<false>, dim3(grid_for(units, 64)), dim3(256), 0,
+  const cudaError_t e = launch_ex(mx_quantize_kernel<0>, dim3(grid_for(units, 64)), dim3(256), 0,
                                   (cudaStream_t)stream, dim3(1, 1, 1), pdl_enabled(),
                                   (const __nv_bfloat16*)x, ldx, (uint8_t*)codes, (uint8_t*)scales, m,
                                   (int)k, (int)((k + 127) / 128));
@@ -411,10 +460,42 @@ extern "C" int mach_swiglu_mxfp8_quantize(const void* gate_up, void* codes, void
       inter > INT32_MAX / 2)
     return fail(MACH_ERR_UNSUPPORTED, "swiglu_mxfp8_quantize: I %% 32 and 16-byte alignment required");
   const int64_t units = m * (inter / 32);
-  mx_quantize_kernel<true><<<grid_for(units, 64), 256, 0, (cudaStream_t)stream>>>(
+  mx_quantize_kernel<1><<<grid_for(units, 64), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)gate_up, 2 * inter, (uint8_t*)codes, (uint8_t*)scales, m, (int)inter,
       (int)((inter + 127) / 128));
   return check_launch("swiglu_mxfp8_quantize");
+}
+
+extern "C" int mach_mxfp8_quantize_weight(const void* w_bf16, void* codes, void* logical_scales,
+                                          int64_t n, int64_t k, void* stream) {
+  if (n < 0 || k < 0) return fail(MACH_ERR_INVALID, "mxfp8_quantize_weight: negative size");
+  if (n == 0 || k == 0) return MACH_OK;
+  if (!w_bf16 || !codes || !logical_scales)
+    return fail(MACH_ERR_INVALID, "mxfp8_quantize_weight: null pointer");
+  if (k % 32 || !aligned16(w_bf16) || !aligned16(codes) || k > INT32_MAX)
+    return fail(MACH_ERR_UNSUPPORTED, "mxfp8_quantize_weight: K %% 32 and 16-byte alignment required");
+  const int64_t units = n * (k / 32);
+  mx_quantize_weight_kernel<<<grid_for(units, 64), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)w_bf16, (uint8_t*)codes, (uint8_t*)logical_scales, n, (int)k);
+  return check_launch("mxfp8_quantize_weight");
+}
+
+extern "C" int mach_swiglu_mxfp8_quantize_champion(const void* gate_up, void* codes, void* scales,
+                                                   int64_t m, int64_t inter, void* stream) {
+  if (m < 0 || inter < 0)
+    return fail(MACH_ERR_INVALID, "swiglu_mxfp8_quantize_champion: negative size");
+  if (m == 0 || inter == 0) return MACH_OK;
+  if (!gate_up || !codes || !scales)
+    return fail(MACH_ERR_INVALID, "swiglu_mxfp8_quantize_champion: null pointer");
+  if (inter % 32 || !aligned16(gate_up) || !aligned16(codes) || m > INT32_MAX ||
+      inter > INT32_MAX / 2)
+    return fail(MACH_ERR_UNSUPPORTED,
+                "swiglu_mxfp8_quantize_champion: I %% 32 and 16-byte alignment required");
+  const int64_t units = m * (inter / 32);
+  mx_quantize_kernel<2><<<grid_for(units, 64), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)gate_up, 2 * inter, (uint8_t*)codes, (uint8_t*)scales, m, (int)inter,
+      (int)((inter + 127) / 128));
+  return check_launch("swiglu_mxfp8_quantize_champion");
 }
 
 namespace mach {

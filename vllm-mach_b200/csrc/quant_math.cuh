@@ -78,4 +78,37 @@ __device__ __forceinline__ float swiglu_bf16(float gate, float up) {
   return bf16_round(__fmul_rn(silu_bf16(gate), up));
 }
 
+// ---- The "champion" SwiGLU producer contract (src/vllm_mach/mxfp8/swiglu_quant.py:46-70): ONE
+// BF16 rounding of silu(gate) * up, the scale exponent from cvt.rp.satfinite.ue8m0x2 of
+// amax * rcp.approx(448), the inverse from rcp.approx of the power of two, and an all-zero
+// block stored as scale byte 0 with inverse 0.
+static __device__ __noinline__ float swiglu_once_slow(float g, float up) {
+  float v = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), up);
+  const int low = static_cast<int>(__float_as_uint(v) & 0xFFFFu);
+  if (abs(low - 0x8000) <= 16) {
+    const float t = static_cast<float>(exp(static_cast<double>(-g)));
+    v = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, t)), up);
+  }
+  return v;
+}
+// bf16( (gate / (1 + exp(-gate))) * up ): the same three tiers as silu_bf16, the tie test
+// applied to the product, which is the only value that is rounded.
+__device__ __forceinline__ float swiglu_once_bf16(float g, float up) {
+  float v = __fmul_rn(__fdividef(g, 1.0f + __expf(-g)), up);
+  const int low = static_cast<int>(__float_as_uint(v) & 0xFFFFu);
+  if (abs(low - 0x8000) <= 96 || fabsf(g) > 32.0f) v = swiglu_once_slow(g, up);
+  return bf16_round(v);
+}
+__device__ __forceinline__ float rcp_approx_ftz(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+// E8M0 byte of the smallest power of two >= raw (0 for raw == 0, 254 at most).
+__device__ __forceinline__ uint32_t ue8m0_round_up(float raw) {
+  uint16_t packed;
+  asm("{cvt.rp.satfinite.ue8m0x2.f32 %0, 0f00000000, %1;}" : "=h"(packed) : "f"(raw));
+  return static_cast<uint32_t>(packed) & 255u;
+}
+
 }  // namespace mach

@@ -167,6 +167,39 @@ def close_all():
         for ws in _workspaces.values():
             ws.close()
         _workspaces.clear()
+        _tensors.clear()
+
+
+# The reference hands its FlashInfer workspace to `mach_norm_quant.run` as an int64 CUDA tensor
+# (a table of 7 device pointers, src/vllm_mach/mxfp6/ar_norm.py:113-128). The same argument
+# carries a B200 workspace: a 7-entry int64 CUDA tensor whose identity (its address) names the
+# ArWorkspace, so the op never reads device memory to find it.
+_tensors: dict = {}
+
+
+def workspace_tensor(group, hidden: int, tokens: int, device) -> torch.Tensor:
+    ws = workspace_for(group, hidden, tokens, device)
+    if ws is None:
+        raise RuntimeError("the fused all-reduce is unavailable for this group or shape")
+    with _lock:
+        for tensor, owner in _tensors.values():
+            if owner is ws:
+                return tensor
+        tensor = torch.zeros(7, dtype=torch.int64, device=ws.device)
+        tensor[0] = ws.handle
+        _tensors[tensor.data_ptr()] = (tensor, ws)
+        return tensor
+
+
+def workspace_from_tensor(tensor: torch.Tensor) -> ArWorkspace:
+    if tensor.dtype != torch.int64 or tensor.numel() != 7 or not tensor.is_contiguous():
+        raise RuntimeError("mach_norm_quant.run requires a contiguous int64 workspace with 7 entries")
+    with _lock:
+        hit = _tensors.get(tensor.data_ptr())
+    if hit is None or hit[1].handle is None:
+        raise RuntimeError("workspace tensor was not created by collective.workspace_tensor "
+                           "(or its workspace has been closed)")
+    return hit[1]
 
 
 def poll_status() -> int:

@@ -29,6 +29,8 @@ _SIGNATURES = {
     "mach_mx_sf_bytes": (ctypes.c_size_t, [_I64, _I64]),
     "mach_mxfp8_quantize": (_INT, [_P, _I64, _P, _P, _I64, _I64, _P]),
     "mach_swiglu_mxfp8_quantize": (_INT, [_P, _P, _P, _I64, _I64, _P]),
+    "mach_swiglu_mxfp8_quantize_champion": (_INT, [_P, _P, _P, _I64, _I64, _P]),
+    "mach_mxfp8_quantize_weight": (_INT, [_P, _P, _P, _I64, _I64, _P]),
     "mach_add_rmsnorm_mxfp8": (_INT, [_P, _P, _P, _F, _F, _P, _P, _P, _P, _I64, _I64, _P]),
     "mach_residual_rmsnorm_rounded_mxfp8": (_INT, [_P, _P, _P, _F, _F, _P, _P, _P, _P, _I64, _I64, _P]),
     "mach_mx_pack_scales": (_INT, [_P, _P, _I64, _I64, _P]),
@@ -71,6 +73,9 @@ _SIGNATURES = {
     "mach_moe_grouped_gemm": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64,
                                      _I64, _INT, _INT, _P]),
     "mach_moe_combine": (_INT, [_P, _P, _P, _P, _I64, _I64, _I64, _P]),
+    "mach_moe_scatter_codes": (_INT, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P]),
+    "mach_moe_stage_offsets": (_INT, [_P, _P, _I64, _P, _P, _P]),
+    "mach_moe_work_from_offsets": (_INT, [_P, _P, _I64, _I64, _I64, _P, _P, _P]),
     "mach_tune_set": (_INT, [ctypes.c_char_p, _INT]),
     "mach_tune_get": (_INT, [ctypes.c_char_p]),
 }
@@ -302,20 +307,27 @@ def fp8_group_quantize(x: torch.Tensor):
     return q, s.t()
 
 
-def silu_mul_fp8_group_quantize(inp: torch.Tensor, transposed: bool = True):
+def silu_mul_fp8_group_quantize(inp: torch.Tensor, transposed: bool = True,
+                                out: torch.Tensor | None = None,
+                                scales: torch.Tensor | None = None):
+    """`out` (E4M3 [M, I]) and `scales` (FP32 [M, I/128], stride (1, M) when transposed) may be
+    supplied by the caller; the kernel then writes straight into them."""
     _require(inp, torch.bfloat16, "input")
     m, two_i = inp.shape
     inter = two_i // 2
-    out = torch.empty((m, inter), dtype=torch.float8_e4m3fn, device=inp.device)
-    if transposed:
-        s = torch.empty((inter // 128, m), dtype=torch.float32, device=inp.device)
+    if out is None:
+        out = torch.empty((m, inter), dtype=torch.float8_e4m3fn, device=inp.device)
+    if scales is not None:
+        view = scales
+    elif transposed:
+        view = torch.empty((inter // 128, m), dtype=torch.float32, device=inp.device).t()
     else:
-        s = torch.empty((m, inter // 128), dtype=torch.float32, device=inp.device)
+        view = torch.empty((m, inter // 128), dtype=torch.float32, device=inp.device)
     with torch.cuda.device(inp.device):
-        _check(lib().mach_silu_mul_fp8_group_quantize(_ptr(inp), _ptr(out), _ptr(s), m, inter,
+        _check(lib().mach_silu_mul_fp8_group_quantize(_ptr(inp), _ptr(out), _ptr(view), m, inter,
                                                       int(transposed), _stream(inp)),
                "silu_mul_fp8_group_quantize")
-    return out, (s.t() if transposed else s)
+    return out, view
 
 
 def block_fp8_gemm(a, sa, b, sb, raw: torch.Tensor | None = None):
