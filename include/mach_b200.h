@@ -106,6 +106,19 @@ MACH_API int mach_residual_rmsnorm_rounded_mxfp8(const void* a_bf16, const void*
                                                  void* residual_out_bf16, void* codes,
                                                  void* scales, int64_t m, int64_t h, void* stream);
 
+/* Gated RMSNorm over 128-wide heads + MXFP8: the producer in front of the linear-attention
+ * output projection. Replaces the producer half of mxfp6.gemm_from_gdn
+ * (src/vllm_mach/mxfp6/gdn_output.py:11-13,56-64; the unfused form is RMSNormGated with
+ * norm_before_gate + SiLU followed by out_proj): per (token, head), rstd = 1/sqrt(mean(x^2)+eps),
+ * v = bf16(((x * rstd) * w) * silu(z)), then the activation quantiser along K = heads * 128.
+ * core BF16 [M, heads, 128] contiguous; gate BF16 with `ld_gate` elements per token;
+ * norm_weight [128] BF16 or FP32. Follow with mach_mx_gemm on the out_proj weight. */
+MACH_API int mach_gated_rmsnorm_mxfp8_quantize(const void* core_bf16, const void* gate_bf16,
+                                               int64_t ld_gate, const void* norm_weight,
+                                               int weight_is_f32, float eps, void* codes,
+                                               void* scales, int64_t m, int64_t heads,
+                                               void* stream);
+
 /* Checkpoint weight quantiser: BF16 [N, K] -> E4M3 codes [N, K] + LOGICAL E8M0 scales uint8
  * [N, K/32], by the rule of quantize_block (src/vllm_mach/mxfp8/reconstruct_model.py:34-50;
  * golden vector tests/test_mxfp8_reconstruct_model.py:142-156): maximum m of the block in BF16,

@@ -190,6 +190,23 @@ def swiglu_quantize_champion(gate_up: torch.Tensor) -> tuple[torch.Tensor, torch
     return codes, byte.to(torch.uint8)
 
 
+def gated_rmsnorm_values(core, gate, weight, eps: float) -> torch.Tensor:
+    """Gated RMSNorm over 128-wide heads (the producer of the linear-attention output
+    projection): core, gate BF16 [M, heads, 128], weight [128] -> BF16 [M, heads * 128].
+
+    The fused form is mxfp6.gemm_from_gdn (src/vllm_mach/mxfp6/gdn_output.py:11-13), in the
+    third-party wheel whose source is absent: PARITY UNPINNED. Restated from the unfused path
+    the reference falls back to (gdn_output.py:62-64: RMSNormGated with norm_before_gate and
+    SiLU, written back as BF16, then out_proj): rstd = 1/sqrt(mean(x^2) + eps),
+    v = bf16(((x * rstd) * w) * (z / (1 + exp(-z)))), one BF16 rounding."""
+    x, z = core.float(), gate.float().reshape(core.shape)
+    variance = (x * x).sum(-1, keepdim=True) / 128.0
+    rstd = 1.0 / torch.sqrt(variance + eps)
+    n = (x * rstd) * weight.float()
+    v = bf16(n * (z / (1.0 + exp_cr(-z))))
+    return v.reshape(core.shape[0], -1).to(torch.bfloat16)
+
+
 # --------------------------------------------------------------------------- norms
 def gemma_rmsnorm(x, residual, weight, eps: float, weight_bias: float = 1.0):
     """Residual + RMSNorm on the UNROUNDED sum.

@@ -132,3 +132,64 @@ def test_champion_swiglu_contract(nat, m, inter):
         ref_codes, ref_scales = ora.swiglu_quantize_champion(x)
         assert torch.equal(ora.unswizzle_scales(scales.cpu(), m, inter), ref_scales), magnitude
         assert torch.equal(codes.cpu(), ref_codes), magnitude
+
+
+@pytest.mark.parametrize("m,heads,wdtype", [(1, 24, torch.bfloat16), (16, 24, torch.float32),
+                                            (33, 3, torch.bfloat16), (513, 24, torch.bfloat16)])
+def test_gated_rmsnorm_producer(nat, m, heads, wdtype):
+    """mach_gated_rmsnorm_mxfp8_quantize vs the oracle's restatement of the unfused gated norm
+    (parity unpinned: the fused form lives in the absent third-party wheel). The sum of 128
+    squares has no canonical order, so a value may differ by one BF16 ulp: fewer than 1 % of
+    the codes differ and never by more than one code; scales equal except where such a value
+    is the block maximum."""
+    core = randn_bf16(m, heads * 128, 900 + m).reshape(m, heads, 128)
+    wide = randn_bf16(m, heads * 128 + 64, 901 + m)       # strided gate rows
+    gate = wide[:, :heads * 128]
+    weight = (1.0 + 0.1 * randn_bf16(1, 128, 902)[0].float()).to(wdtype)
+    codes, scales = nat.gated_rmsnorm_quantize(core.cuda(), wide.cuda()[:, :heads * 128],
+                                               weight.cuda(), 1e-6)
+    torch.cuda.synchronize()
+    values = ora.gated_rmsnorm_values(core, gate.contiguous().reshape(m, heads, 128), weight, 1e-6)
+    ref_codes, ref_scales = ora.quantize_mxfp8(values)
+    got_scales = ora.unswizzle_scales(scales.cpu(), m, heads * 128)
+    assert float((got_scales != ref_scales).float().mean()) < 0.01
+    same_scale = (got_scales == ref_scales).repeat_interleave(32, 1)
+    got, ref = codes.view(torch.uint8).cpu(), ref_codes
+    differ = (got != ref) & same_scale
+    assert float(differ.float().mean()) < 0.01
+    step = (got.to(torch.int16) - ref.to(torch.int16)).abs()
+    assert int(step[differ].max() if differ.any() else 0) <= 1
+
+
+def test_gdn_output_projection_and_projected_adapter(nat):
+    """vllm::mach_gdn_norm_mxfp6_out at the reference's shape (24 heads of 128 -> 5120,
+    src/vllm_mach/mxfp6/gdn_output.py:21-33) and `projected` at its QKV-like shapes."""
+    from mach_b200 import ops
+    ops.register()
+    ops.set_mxfp6_format("e3m2")
+    m, heads, n = 8, 24, 5120
+    k = heads * 128
+    core = randn_bf16(m, k, 950).reshape(m, heads, 128)
+    gate = randn_bf16(m, k, 951)
+    weight = (1.0 + 0.1 * randn_bf16(1, 128, 952)[0].float()).bfloat16()
+    w = randn_bf16(n, k, 953, 0.02)
+    w_codes, w_scales = ora.quantize_weight_mxfp6(w, "e3m2")
+    packed_w = ora.pack_fp6(w_codes).cuda()
+    packed_s = nat.pack_scales(w_scales.cuda(), k)
+    out = torch.ops.vllm.mach_gdn_norm_mxfp6_out(core.cuda(), gate.cuda(), weight.cuda(), packed_w,
+                                                 packed_s, 1e-6)
+    values = ora.gated_rmsnorm_values(core, gate.reshape(m, heads, 128), weight, 1e-6)
+    a_c, a_s = ora.quantize_mxfp8(values)
+    ref = ora.mx_gemm(a_c, a_s, ora.dequantize_mxfp6(w_codes, w_scales, "e3m2"))
+    assert out.shape == (m, n)
+    assert torch.allclose(out.float().cpu(), ref.float(), rtol=0.01, atol=0.02)
+    # projected(): activations already quantised by a fused norm
+    for (rows, n2, k2) in ((4, 8192, 5120), (32, 3840, 5120)):
+        x = randn_bf16(rows, k2, 960 + rows)
+        w2 = randn_bf16(n2, k2, 961 + rows, 0.02)
+        c2, s2 = ora.quantize_weight_mxfp6(w2, "e3m2")
+        codes, scales = nat.quantize_mxfp8(x.cuda())
+        y = ops.projected(codes, scales, ora.pack_fp6(c2).cuda(), nat.pack_scales(s2.cuda(), k2))
+        rc, rs = ora.quantize_mxfp8(x)
+        ref2 = ora.mx_gemm(rc, rs, ora.dequantize_mxfp6(c2, s2, "e3m2"))
+        assert torch.allclose(y.float().cpu(), ref2.float(), rtol=0.01, atol=0.02)

@@ -141,6 +141,56 @@ mx_quantize_weight_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restri
   }
 }
 
+
+// Gated RMSNorm over 128-wide heads + MXFP8 quantisation: the producer in front of the
+// linear-attention output projection (gemm_from_gdn, src/vllm_mach/mxfp6/gdn_output.py:11-13,56-64;
+// unfused form: RMSNormGated with norm_before_gate and SiLU, then out_proj):
+//   rstd = 1 / sqrt(mean_128(x^2) + eps);  n = (x * rstd) * w;  v = bf16(n * (z / (1 + exp(-z))))
+// followed by the activation quantiser on v along K = heads * 128. Sixteen threads per
+// (token, head), eight values each; the sum of squares is a fixed shuffle tree.
+template <typename W>
+__global__ void __launch_bounds__(256)
+gated_rmsnorm_mx_kernel(const __nv_bfloat16* __restrict__ core, const __nv_bfloat16* __restrict__ gate,
+                        int64_t ld_gate, const W* __restrict__ weight, float eps,
+                        uint8_t* __restrict__ codes, uint8_t* __restrict__ scales, int64_t m,
+                        int heads, int k_tiles) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane16 = threadIdx.x & 15;
+  const int64_t units = m * heads;
+  const int k = heads * 128;
+  float w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) w[i] = static_cast<float>(weight[lane16 * 8 + i]);
+  for (int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 4);
+       unit < ((units + 1) & ~(int64_t)1); unit += (int64_t)gridDim.x * (blockDim.x >> 4)) {
+    const bool valid = unit < units;   // units are paired in a warp: keep both halves in step
+    const int64_t row = valid ? unit / heads : 0;
+    const int head = valid ? (int)(unit - row * heads) : 0;
+    float x[8], z[8];
+    unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(core + row * k + head * 128 + lane16 * 8)), x);
+    unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(gate + row * ld_gate + head * 128 + lane16 * 8)), z);
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sq = __fadd_rn(sq, __fmul_rn(x[i], x[i]));
+#pragma unroll
+    for (int d = 8; d > 0; d >>= 1) sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, d));
+    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sq, 128.0f), eps)));
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      v[i] = swiglu_once_bf16(z[i], __fmul_rn(__fmul_rn(x[i], rstd), w[i]));
+    const float amax = amax8_quad(v);
+    const uint32_t bits = mx_scale_bits(amax);
+    const float inv = mx_inverse(bits);
+    if (valid) {
+      *reinterpret_cast<uint2*>(codes + row * k + head * 128 + lane16 * 8) = quantize8(v, inv);
+      if ((lane16 & 3) == 0)
+        scales[sf_offset((int)row, head * 4 + (lane16 >> 2), k_tiles)] = (uint8_t)(bits >> 23);
+    }
+  }
+}
+
 // One CTA per row; thread t owns elements [8t, 8t+8) (+ 8*blockDim per extra vector).
 template <int kVecs>
 __global__ void __launch_bounds__(1024)
@@ -464,6 +514,40 @@ extern "C" int mach_swiglu_mxfp8_quantize(const void* gate_up, void* codes, void
       (const __nv_bfloat16*)gate_up, 2 * inter, (uint8_t*)codes, (uint8_t*)scales, m, (int)inter,
       (int)((inter + 127) / 128));
   return check_launch("swiglu_mxfp8_quantize");
+}
+
+extern "C" int mach_gated_rmsnorm_mxfp8_quantize(const void* core_bf16, const void* gate_bf16,
+                                                 int64_t ld_gate, const void* norm_weight,
+                                                 int weight_is_f32, float eps, void* codes,
+                                                 void* scales, int64_t m, int64_t heads,
+                                                 void* stream) {
+  if (m < 0 || heads < 0) return fail(MACH_ERR_INVALID, "gated_rmsnorm_mxfp8: negative size");
+  if (m == 0 || heads == 0) return MACH_OK;
+  if (!core_bf16 || !gate_bf16 || !norm_weight || !codes || !scales)
+    return fail(MACH_ERR_INVALID, "gated_rmsnorm_mxfp8: null pointer");
+  if (!aligned16(core_bf16) || !aligned16(gate_bf16) || !aligned16(codes) || ld_gate % 8 ||
+      ld_gate < heads * 128 || m > INT32_MAX || heads > 4096)
+    return fail(MACH_ERR_UNSUPPORTED,
+                "gated_rmsnorm_mxfp8: 16-byte aligned rows of heads x 128 required");
+  const int64_t units = m * heads;
+  const int blocks = (int)std::max<int64_t>(1, std::min<int64_t>((units + 15) / 16, (int64_t)sm_count() * 8));
+  const int k_tiles = (int)heads;   // K = heads * 128
+  cudaError_t e;
+  if (weight_is_f32)
+    e = launch_ex(gated_rmsnorm_mx_kernel<float>, dim3((unsigned)blocks), dim3(256), 0,
+                  (cudaStream_t)stream, dim3(1, 1, 1), pdl_enabled(),
+                  (const __nv_bfloat16*)core_bf16, (const __nv_bfloat16*)gate_bf16, ld_gate,
+                  (const float*)norm_weight, eps, (uint8_t*)codes, (uint8_t*)scales, m, (int)heads,
+                  k_tiles);
+  else
+    e = launch_ex(gated_rmsnorm_mx_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0,
+                  (cudaStream_t)stream, dim3(1, 1, 1), pdl_enabled(),
+                  (const __nv_bfloat16*)core_bf16, (const __nv_bfloat16*)gate_bf16, ld_gate,
+                  (const __nv_bfloat16*)norm_weight, eps, (uint8_t*)codes, (uint8_t*)scales, m,
+                  (int)heads, k_tiles);
+  if (e != cudaSuccess)
+    return fail(MACH_ERR_CUDA, "gated_rmsnorm_mxfp8: %s", cudaGetErrorString(e));
+  return MACH_OK;
 }
 
 extern "C" int mach_mxfp8_quantize_weight(const void* w_bf16, void* codes, void* logical_scales,

@@ -31,6 +31,7 @@ _SIGNATURES = {
     "mach_swiglu_mxfp8_quantize": (_INT, [_P, _P, _P, _I64, _I64, _P]),
     "mach_swiglu_mxfp8_quantize_champion": (_INT, [_P, _P, _P, _I64, _I64, _P]),
     "mach_mxfp8_quantize_weight": (_INT, [_P, _P, _P, _I64, _I64, _P]),
+    "mach_gated_rmsnorm_mxfp8_quantize": (_INT, [_P, _P, _I64, _P, _INT, _F, _P, _P, _I64, _I64, _P]),
     "mach_add_rmsnorm_mxfp8": (_INT, [_P, _P, _P, _F, _F, _P, _P, _P, _P, _I64, _I64, _P]),
     "mach_residual_rmsnorm_rounded_mxfp8": (_INT, [_P, _P, _P, _F, _F, _P, _P, _P, _P, _I64, _I64, _P]),
     "mach_mx_pack_scales": (_INT, [_P, _P, _I64, _I64, _P]),
@@ -193,6 +194,33 @@ def add_rmsnorm_mxfp8(x, residual, weight, eps: float, weight_bias: float = 1.0,
         _check(fn(_ptr(x), _ptr(residual), _ptr(weight), eps, weight_bias, _ptr(norm),
                   _ptr(res_out), _ptr(codes), _ptr(scales), m, h, _stream(x)), "add_rmsnorm_mxfp8")
     return norm, res_out, codes, scales
+
+
+def gated_rmsnorm_quantize(core: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float):
+    """core BF16 [M, heads, 128]; gate BF16 [M, heads, 128] (rows may be strided); weight [128]
+    BF16 or FP32 -> (E4M3 codes [M, heads * 128], swizzled E8M0 scales)."""
+    _require(core, torch.bfloat16, "core")
+    if core.ndim != 3 or core.shape[2] != 128:
+        raise ValueError("core must be [M, heads, 128]")
+    m, heads, _ = core.shape
+    gate2 = gate.reshape(m, -1) if gate.is_contiguous() else gate
+    if gate2.dtype != torch.bfloat16 or gate2.shape[-1] != heads * 128 and gate2.ndim == 2:
+        raise ValueError("gate must be BF16 [M, heads * 128]")
+    if gate2.ndim == 3:
+        gate2 = gate2.reshape(m, heads * 128)
+    if gate2.stride(-1) != 1:
+        raise ValueError("gate rows must be dense")
+    if weight.dtype not in (torch.bfloat16, torch.float32) or weight.numel() != 128:
+        raise ValueError("norm weight must be BF16 or FP32 [128]")
+    k = heads * 128
+    codes = torch.empty((m, k), dtype=torch.float8_e4m3fn, device=core.device)
+    scales = torch.empty((sf_bytes(m, k),), dtype=torch.uint8, device=core.device)
+    with torch.cuda.device(core.device):
+        _check(lib().mach_gated_rmsnorm_mxfp8_quantize(
+            _ptr(core), _ptr(gate2), gate2.stride(0) if m > 1 else k, _ptr(weight.contiguous()),
+            int(weight.dtype == torch.float32), eps, _ptr(codes), _ptr(scales), m, heads,
+            _stream(core)), "gated_rmsnorm_mxfp8_quantize")
+    return codes, scales
 
 
 def pack_scales(logical: torch.Tensor, k: int) -> torch.Tensor:

@@ -178,6 +178,24 @@ def _norm_quant_run(hidden, residual, gamma, workspace, norm, residual_out, quan
             m, h, 0, native._stream(hidden)), "mach_norm_quant.run")
 
 
+def _gdn_norm_out(core, gate, norm_weight, weight, weight_scale, eps: float):
+    """vllm::mach_gdn_norm_mxfp6_out (src/vllm_mach/mxfp6/gdn_output.py:11-19,56-64): gated
+    RMSNorm + MXFP8 producer, then the W6A8 output projection."""
+    codes, scales = native.gated_rmsnorm_quantize(core, gate, norm_weight, eps)
+    if core.shape[0] == 0:
+        return core.new_empty((0, weight.shape[0]))
+    return native.mx_gemm(codes, scales, weight.view(torch.uint8), weight_scale,
+                          current_mxfp6_format())
+
+
+def projected(codes, scales, weight, weight_scale, fmt: str | None = None):
+    """The reference's `projected(codes, scales, layer)` (src/vllm_mach/mxfp6/ar_norm.py:144-147):
+    a projection fed by activations that a fused norm already quantised (QKV / QKVZ / gate_up
+    after the all-reduce + norm + MXFP8 kernel)."""
+    return native.mx_gemm(codes, scales, weight.view(torch.uint8), weight_scale,
+                          fmt or current_mxfp6_format())
+
+
 # ---- mixture-of-experts shims (src/vllm_mach/mxfp6/moe_utils.py:47-488)
 def _moe_quantize_mxfp8(input):
     codes, scales = native.quantize_mxfp8(input)
@@ -267,6 +285,9 @@ _SCHEMAS = [
     ("vllm_mach_fp8", "silu_and_mul_per_block_quant(Tensor(a!) out, Tensor input, Tensor(b!) scales, "
                       "int group_size, Tensor? scale_ub, bool is_scale_transposed) -> ()",
      _silu_and_mul_per_block_quant, lambda *a: None),
+    ("vllm", "mach_gdn_norm_mxfp6_out(Tensor core, Tensor gate, Tensor norm_weight, Tensor weight, "
+             "Tensor weight_scale, float eps) -> Tensor",
+     _gdn_norm_out, lambda c, g, nw, w, ws, eps: c.new_empty((c.shape[0], w.shape[0]))),
     ("mach_fp8_activation", "run(Tensor(a!) out, Tensor input, Tensor(b!) scales, "
                             "bool is_scale_transposed) -> ()",
      _fp8_activation_run, lambda *a: None),
