@@ -53,6 +53,18 @@ def _worker(rank, world, port, out):
         full_norm, full_res = ora.allreduce_rmsnorm([mlp(0, inter)], residual, gamma, 1e-6)
         rel = float((norm.float() - full_norm.float()).norm() / full_norm.float().norm())
         assert rel < 2e-2, rel
+        # Row ownership between norms: the blocks tile [0, m) in rank order, and gathering every
+        # rank's owned rows of the residual stream gives back the full tensor.
+        first, count = collective.owner_rows(m, dist.group.WORLD)
+        spans = [None] * world
+        dist.all_gather_object(spans, (first, count))
+        assert spans[0][0] == 0 and spans[-1][0] + spans[-1][1] == m
+        assert all(a[0] + a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        owned = res[first:first + count].contiguous()
+        assert torch.equal(collective.gather_owned_rows(owned, m, dist.group.WORLD), res)
+        for tokens in (0, 1, 7, 4096):
+            f, c = collective.owner_rows(tokens, dist.group.WORLD)
+            assert 0 <= f <= tokens and f + c <= tokens and c <= (tokens + world - 1) // world
         out[rank] = (res.float().sum().item(), rel)
     finally:
         dist.destroy_process_group()
