@@ -433,6 +433,36 @@ def run_gpu(args):
     ev_out = [torch.cuda.Event() for _ in range(2)]      # download into host buffer b finished
     keep = [None, None]
 
+    # The device part of a step is captured once per (input buffer, weight set) in a CUDA graph
+    # and replayed, as a serving engine does: at N >= 4 the kernels of a step take less time
+    # than the Python and ctypes calls that launch them one by one.
+    graphs = {}
+    if not args.no_e2e_graphs:
+        try:
+            side = torch.cuda.Stream(device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                for b in range(2):
+                    for w in range(NUM_WEIGHT_SETS):
+                        tp_step(dev_in[b], residual, residual_rows, gamma, sets[w], group, owner)
+            main.wait_stream(side)
+            barrier()
+            for b in range(2):
+                for w in range(NUM_WEIGHT_SETS):
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        result = tp_step(dev_in[b], residual, residual_rows, gamma, sets[w], group,
+                                         owner)
+                    graphs[(b, w)] = (graph, result)
+            barrier()
+        except RuntimeError:
+            graphs = {}
+    flag = torch.tensor([1.0 if graphs else 0.0], device=device)
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)   # every rank takes the same route
+    if flag.item() == 0.0:
+        graphs = {}
+
     def e2e_steps(count_steps):
         for st in (s_in, s_run, s_out):
             st.wait_stream(main)
@@ -449,8 +479,16 @@ def run_gpu(args):
                 ev_in[b].record(s_in)
             with torch.cuda.stream(s_run):
                 s_run.wait_event(ev_in[b])
-                result = tp_step(dev_in[b], residual, residual_rows, gamma,
-                                 sets[i % NUM_WEIGHT_SETS], group, owner)
+                if graphs:
+                    # the graph's output buffer is reused by its next replay: wait for the
+                    # download that still reads it
+                    if i >= 2:
+                        s_run.wait_event(ev_out[b])
+                    graph, result = graphs[(b, i % NUM_WEIGHT_SETS)]
+                    graph.replay()
+                else:
+                    result = tp_step(dev_in[b], residual, residual_rows, gamma,
+                                     sets[i % NUM_WEIGHT_SETS], group, owner)
                 norm = result[0]
                 ev_free[b].record(s_run)
                 ev_done[b].record(s_run)
@@ -458,7 +496,8 @@ def run_gpu(args):
                 s_out.wait_event(ev_done[b])
                 if i >= 2:
                     s_out.wait_event(ev_out[b])
-                norm.record_stream(s_out)
+                if not graphs:
+                    norm.record_stream(s_out)
                 if owner:
                     host_out[b][rows_lo:rows_hi].copy_(norm, non_blocking=True)
                 elif even_split:
@@ -547,9 +586,11 @@ def run_gpu(args):
                              f"({NUM_WEIGHT_SETS * sets[0].nbytes() * world / 1e6:.0f} MB > 126 MB L2)"},
             "e2e": {"value": m * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": m * HIDDEN * 2, "d2h_bytes_per_step": m * HIDDEN * 2,
-                    "note": "bytes over all ranks; each rank moves the rows it owns and the "
-                            "ranks all-gather the input over NVLink" if world > 1 else
-                            "upload, kernels and download on three streams, double-buffered"},
+                    "note": ("bytes over all ranks; each rank moves the rows it owns and the "
+                             "ranks all-gather the input over NVLink" if world > 1 else
+                             "upload, kernels and download on three streams, double-buffered")
+                            + ("; device part of the step replayed from a CUDA graph" if graphs
+                               else "; kernels launched one by one")},
             "gpu_launches": 4 * args.steps,
             "roofline": roofline,
             "clocks": clocks, "device_status": status,
@@ -990,6 +1031,8 @@ def main():
     ap.add_argument("--no-tp-suite", action="store_true",
                     help="skip the MXFP6 MLP / MoE tensor-parallel timings")
     ap.add_argument("--no-library", action="store_true", help="skip the cuBLASLt FP8 peak")
+    ap.add_argument("--no-e2e-graphs", action="store_true",
+                    help="end-to-end leg: launch the kernels one by one instead of replaying graphs")
     ap.add_argument("--no-owner", action="store_true",
                     help="N >= 2: push-form reduce with all rows on every rank")
     ap.add_argument("--suite", default=None,

@@ -213,3 +213,33 @@ def test_bounded_wait_runs_out_and_reset_recovers(owner):
         _check_codes("after reset", outs[1][2], outs[1][3], norm_full, m, h)
     finally:
         group.close()
+
+
+@pytest.mark.parametrize("h", [2560, 5120, 8192])
+def test_owner_form_single_rank_prefetch_path(h):
+    """One rank owns every row: the per-rank kernel (with the next-row prefetch for hidden <=
+    4096, without it above) instead of the single-grid multi-rank launch."""
+    from mach_b200 import native
+    group = LocalRanks(1, h, 2048)
+    lib = group.lib
+    try:
+        for it, m in enumerate((1, 700, 2048)):
+            partials, residual, gamma = _inputs(1, m, h, 1234 + it + h)
+            ref_norm, ref_res = ora.allreduce_rmsnorm(partials, residual, gamma, EPS)
+            x, res_in, g = partials[0].cuda(), residual.cuda(), gamma.cuda()
+            if it % 2:
+                group.partial_buffer(0, m).copy_(x)
+            norm, res = torch.empty_like(x), torch.empty_like(x)
+            codes = torch.empty((m, h), dtype=torch.uint8, device="cuda")
+            scales = torch.empty(native.sf_bytes(m, h), dtype=torch.uint8, device="cuda")
+            rc = lib.mach_allreduce_owner_rmsnorm_mxfp8(
+                group.handles[0], None if it % 2 else x.data_ptr(), res_in.data_ptr(), g.data_ptr(),
+                EPS, 1.0, norm.data_ptr(), res.data_ptr(), codes.data_ptr(), scales.data_ptr(), m, h,
+                ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+            native._check(rc, "allreduce_owner")
+            torch.cuda.synchronize()
+            assert native.device_status() == 0
+            _check_rows(f"owner world1 h{h} m{m}", norm, res, ref_norm, ref_res)
+            _check_codes(f"owner world1 h{h} m{m}", codes, scales, norm, m, h)
+    finally:
+        group.close()

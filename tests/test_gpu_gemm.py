@@ -58,7 +58,7 @@ def test_mx_gemm_edge_magnitudes(nat):
     assert torch.allclose(out.float(), ref.float(), rtol=0.01, atol=0.02)
 
 
-@pytest.mark.parametrize("split", [1, 2, 4, 8])
+@pytest.mark.parametrize("split", [1, 2, 3, 4, 5, 7, 8])
 def test_feature_major_split_k_is_deterministic_and_correct(nat, split):
     nat.tune("split", split)
     try:

@@ -300,6 +300,7 @@ __device__ __forceinline__ RowOut full_row_out(const ArParams& p, int row) {
 }
 
 // ------------------------------------------------------------------ owner form
+template <bool kPrefetch>
 __device__ __forceinline__ void owner_body(const ArParams& p, uint8_t* mine, uint32_t* ctrl,
                                            uint32_t target, bool failed_before, float* warp_sums) {
   const int cta = blockIdx.x, ctas = gridDim.x;
@@ -332,31 +333,46 @@ __device__ __forceinline__ void owner_body(const ArParams& p, uint8_t* mine, uin
   }
   if (!poison) poison = wait_peers(p, mine, false, 0, target, kWaitScatter);
 
-  // ---- (1) my rows: pull from every rank, sum in rank order, residual + norm + quant
+  // ---- (1) my rows: pull from every rank, sum in rank order, residual + norm + quant.
+  // With kPrefetch the loads of the CTA's NEXT row are issued before the current row is
+  // reduced and normalised, so the NVLink round trip of one row hides behind the arithmetic
+  // (and the block barriers) of another; rows of one CTA are otherwise strictly sequential.
   uint8_t* stage_codes = mine + p.owner_stage_off;
   uint8_t* stage_scales = stage_codes + (size_t)p.m * p.h;
+  auto issue = [&](int j, uint4 (&v)[kMaxWorld]) {
+    const int row = first + j;
+#pragma unroll
+    for (int src = 0; src < kMaxWorld; ++src) {
+      if (src < p.world) {
+        if (src == p.rank && p.partial)
+          v[src] = *reinterpret_cast<const uint4*>(p.partial + (size_t)row * p.h + col);
+        else
+          v[src] = ld_peer16(p.peers[src] + p.owner_partial_off + (size_t)row * row_bytes +
+                             (size_t)col * 2);
+      }
+    }
+  };
+  const bool loads = have && !poison;
+  uint4 cur[kMaxWorld], nxt[kMaxWorld];
+  if (kPrefetch && loads && cta < count) issue(cta, cur);
   for (int j = cta; j < count; j += ctas) {
     const int row = first + j;
+    if (loads) {
+      if (kPrefetch) {
+        if (j + ctas < count) issue(j + ctas, nxt);
+      } else {
+        issue(j, cur);
+      }
+    }
     float a[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) a[i] = 0.0f;
-    if (have && !poison) {
-      uint4 v[kMaxWorld];
-#pragma unroll
-      for (int src = 0; src < kMaxWorld; ++src) {
-        if (src < p.world) {
-          if (src == p.rank && p.partial)
-            v[src] = *reinterpret_cast<const uint4*>(p.partial + (size_t)row * p.h + col);
-          else
-            v[src] = ld_peer16(p.peers[src] + p.owner_partial_off + (size_t)row * row_bytes +
-                               (size_t)col * 2);
-        }
-      }
+    if (loads) {
 #pragma unroll
       for (int src = 0; src < kMaxWorld; ++src) {
         if (src < p.world) {
           float f[8];
-          unpack8(v[src], f);
+          unpack8(cur[src], f);
 #pragma unroll
           for (int i = 0; i < 8; ++i) a[i] = __fadd_rn(a[i], f[i]);
         }
@@ -373,6 +389,10 @@ __device__ __forceinline__ void owner_body(const ArParams& p, uint8_t* mine, uin
     o.scales2 = stage_scales + (size_t)j * groups;
     o.scale_row = row;
     norm_row(p, p.residual + (size_t)j * p.h, o, col, have, poison, a, warp_sums);
+    if (kPrefetch) {
+#pragma unroll
+      for (int src = 0; src < kMaxWorld; ++src) cur[src] = nxt[src];
+    }
   }
   if (!failed_before) {
     // also after a late scatter flag: the peers still expect this rank's gather flag
@@ -622,6 +642,7 @@ __device__ __forceinline__ void push_body(const ArParams& p, uint8_t* mine, uint
   }
 }
 
+template <bool kPrefetch>
 __device__ __forceinline__ void ar_body(const ArParams& p) {
   __shared__ float warp_sums[33];
   __shared__ uint32_t s_epoch, s_failed;
@@ -635,7 +656,7 @@ __device__ __forceinline__ void ar_body(const ArParams& p) {
   const uint32_t epoch = s_epoch;
   const bool failed_before = s_failed != 0;
   if (failed_before && blockIdx.x == 0 && threadIdx.x == 0) report_timeout(p.status, kWorkspaceFailed);
-  if (p.owner) owner_body(p, mine, ctrl, epoch + 1, failed_before, warp_sums);
+  if (p.owner) owner_body<kPrefetch>(p, mine, ctrl, epoch + 1, failed_before, warp_sums);
   else push_body(p, mine, ctrl, epoch, failed_before, warp_sums);
 
   // ---- the last CTA to finish advances the epoch for the next launch
@@ -652,11 +673,15 @@ __device__ __forceinline__ void ar_body(const ArParams& p) {
 }
 
 // blockDim.x == ceil(h / 8) rounded up to a warp: one 16-byte vector per thread per row.
-__global__ void __launch_bounds__(1024)
+// Two instantiations: up to 512 threads (hidden <= 4096) leaves 128 registers per thread,
+// enough to hold the next row's peer loads while the current row is processed; hidden up to
+// 8192 needs 1024 threads and runs without that prefetch.
+template <int kMaxThreads>
+__global__ void __launch_bounds__(kMaxThreads)
 allreduce_norm_kernel(const ArParams p) {
   pdl_launch_dependents();
   pdl_wait();  // the partial sums come from the preceding GEMM
-  ar_body(p);
+  ar_body<(kMaxThreads <= 512)>(p);
 }
 
 // Every rank of a group whose buffers all live on this device, as ONE cooperative grid:
@@ -664,7 +689,7 @@ allreduce_norm_kernel(const ArParams p) {
 // one GPU, so this is how the multi-rank protocols run where there are fewer GPUs than ranks.
 __global__ void __launch_bounds__(1024)
 allreduce_norm_local_ranks_kernel(const __grid_constant__ ArParamsMulti all) {
-  ar_body(all.r[blockIdx.y]);
+  ar_body<false>(all.r[blockIdx.y]);
 }
 
 size_t parity_bytes_for(int world, int64_t tokens_cap, int64_t hidden) {
@@ -780,8 +805,11 @@ int resident_ctas(int threads, bool local_ranks) {
   const cudaError_t e =
       local_ranks ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(
                         &per_sm, allreduce_norm_local_ranks_kernel, threads, 0)
-                  : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_norm_kernel,
-                                                                  threads, 0);
+                  : threads <= 512
+                        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                              &per_sm, allreduce_norm_kernel<512>, threads, 0)
+                        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                              &per_sm, allreduce_norm_kernel<1024>, threads, 0);
   if (e != cudaSuccess || per_sm < 1) return 0;
   return per_sm * sm_count();
 }
@@ -821,9 +849,13 @@ int launch_rank(const ArParams& p, cudaStream_t stream) {
   // Forms whose CTAs wait on flags published by the grid's last CTA are launched cooperatively:
   // a grid that cannot be co-resident (another stream holds the SMs) is then held back or
   // refused by the driver instead of spinning until its waits give up.
+  const bool pdl = needs_resident ? false : pdl_enabled();
   const cudaError_t e =
-      launch_ex_attrs(allreduce_norm_kernel, dim3((unsigned)ctas), dim3(threads), 0, stream,
-                      dim3(1, 1, 1), needs_resident ? false : pdl_enabled(), needs_resident, p);
+      threads <= 512
+          ? launch_ex_attrs(allreduce_norm_kernel<512>, dim3((unsigned)ctas), dim3(threads), 0,
+                            stream, dim3(1, 1, 1), pdl, needs_resident, p)
+          : launch_ex_attrs(allreduce_norm_kernel<1024>, dim3((unsigned)ctas), dim3(threads), 0,
+                            stream, dim3(1, 1, 1), pdl, needs_resident, p);
   if (e != cudaSuccess) return fail(MACH_ERR_CUDA, "allreduce_rmsnorm: %s", cudaGetErrorString(e));
   return MACH_OK;
 }

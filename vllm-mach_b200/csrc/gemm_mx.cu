@@ -88,10 +88,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   const int stage_bytes = (sf_off + (kNumP + num_q_sf) * kSfAtom + 1023) & ~1023;
   const int stages = p.stages;
   const int split = kSwap ? p.split : 1;
-  const int cols_owned = bn / split;  // token columns of the tile this CTA finalises
+  // token columns of the tile this CTA finalises (the last CTAs of an odd-sized cluster own
+  // fewer, possibly none)
+  const int cols_owned = (bn + split - 1) / split;
 
   float* recv = reinterpret_cast<float*>(smem + (size_t)stages * stage_bytes);
-  const int recv_bytes = kSwap ? kNumP * kTileRows * bn * 4 : 0;
+  const int recv_bytes = kSwap ? kNumP * kTileRows * split * cols_owned * 4 : 0;
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(recv) + recv_bytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 1);
   const uint32_t full0 = smem_u32(bars);
@@ -693,8 +695,8 @@ int run_mx_gemm(const void* a_codes, const void* a_sf, const void* w, const void
     }
     split = std::min(split, max_split);
     while (split > 1 && split > prm.k_tiles) split >>= 1;
-    if (split != 1 && split != 2 && split != 4 && split != 8)
-      return fail(MACH_ERR_INVALID, "%s: cluster split must be 1, 2, 4 or 8", what);
+    if (split < 1 || split > max_split)
+      return fail(MACH_ERR_INVALID, "%s: cluster split must be 1..8", what);
     prm.split = split;
     grid = dim3((unsigned)tiles, (unsigned)split, 1);
     prm.stream_weights = 1;
@@ -729,7 +731,9 @@ int run_mx_gemm(const void* a_codes, const void* a_sf, const void* w, const void
   // Shared memory plan: [stages][recv][barriers + TMEM slot] (+ 1 KiB alignment slack).
   const int tx = num_p * kTileBytes + bn * kTileK + (num_p + num_q_sf) * kSfAtom;
   const int stage_bytes = (tx + 1023) & ~1023;
-  const int recv_bytes = swap ? num_p * kTileRows * bn * 4 : 0;
+  // receive slots: [tile][source rank][owned column][128 rows]; sized for the largest cluster
+  // the heuristic below may still shrink to, so the plan does not depend on that choice
+  const int recv_bytes = swap ? num_p * kTileRows * (bn + 7) * 4 : 0;
   const int fixed = recv_bytes + (2 * kMaxStages + 1) * 8 + 16 + 1024;
   int budget = max_smem_optin();
   // Feature-major CTAs stay small (three per SM) so that every CTA of the grid is resident at
@@ -758,7 +762,8 @@ int run_mx_gemm(const void* a_codes, const void* a_sf, const void* w, const void
       prm.stages = stages;
       smem_bytes = stages * stage_bytes + fixed;
     }
-    while (prm.split > 1 && tiles * prm.split > resident(stages)) prm.split >>= 1;
+    while (prm.split > 1 && tiles * prm.split > resident(stages))
+      prm.split = prm.split > 2 && (prm.split & (prm.split - 1)) ? prm.split - 1 : prm.split >> 1;
     grid = dim3((unsigned)tiles, (unsigned)prm.split, 1);
   }
   // Co-resident CTAs must never over-subscribe TMEM: a CTA blocked in tcgen05.alloc while a
