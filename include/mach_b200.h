@@ -381,7 +381,8 @@ MACH_API int mach_moe_work_from_offsets(const void* expert_offsets_i64,
                                         void* num_work, void* stream);
 
 /* Tuning / experiment knobs (process-global, not thread-safe; 0 restores the heuristic):
- * "split" (cluster size along K of the feature-major GEMM: 1, 2, 4, 8), "stages" (pipeline
+ * "split" (cluster size along K of the feature-major GEMM: 1..8), "split_fill_pct" (grow the
+ * cluster until CTAs reach this percentage of the SM count), "stages" (pipeline
  * depth), "bn" (token-major N tile: 128, 256), "swap_max_m" (largest batch handled
  * feature-major, <= 64), "smem_cap_kb" (cap on dynamic shared memory per CTA), "tm_min_m"
  * (smallest batch for the persistent 256-token kernels), "tm_bn" (their tile width), "pair"

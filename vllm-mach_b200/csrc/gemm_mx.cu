@@ -526,6 +526,7 @@ namespace {
 
 struct Tuning {
   int force_split = 0;     // feature-major cluster size (0 = heuristic)
+  int split_fill_pct = 0;  // heuristic: grow the cluster until CTAs >= this % of the SM count (0 = choose)
   int force_stages = 0;    // pipeline depth (0 = fill shared memory)
   int force_bn = 0;        // token-major N tile (0 = heuristic)
   int swap_max_m = 256;    // largest batch handled feature-major (further limited by shape)
@@ -691,7 +692,12 @@ int run_mx_gemm(const void* a_codes, const void* a_sf, const void* w, const void
     } else {
       // Measured on B200: about two CTAs per SM (each with a short ring) stream weights faster
       // than one CTA per SM with a deep ring, and finer pieces balance better over 148 SMs.
-      while (split < max_split && tiles * split < 2 * sm_count()) split <<= 1;
+      // Fewer tiles than SMs (narrow N): stop at 1.25 CTAs per SM. Measured on B200, 6144 x 2048
+      // at M = 16: 5.3 us with 4 CTAs per cluster (192 CTAs) against 6.3 us with 8 (384); with
+      // at least one tile per SM the second CTA per SM pays (34816 x 5120: 25.7 us against 29).
+      const int fill_pct = g_tune.split_fill_pct > 0 ? g_tune.split_fill_pct
+                                                     : (tiles >= sm_count() ? 200 : 125);
+      while (split < max_split && tiles * split * 100 < (int64_t)fill_pct * sm_count()) split <<= 1;
     }
     split = std::min(split, max_split);
     while (split > 1 && split > prm.k_tiles) split >>= 1;
@@ -840,6 +846,7 @@ extern "C" int mach_tune_set(const char* name, int value) {
   using mach::g_tune;
   if (!name) return mach::fail(MACH_ERR_INVALID, "tune_set: null name");
   if (!strcmp(name, "split")) g_tune.force_split = value;
+  else if (!strcmp(name, "split_fill_pct")) g_tune.split_fill_pct = value;
   else if (!strcmp(name, "stages")) g_tune.force_stages = value;
   else if (!strcmp(name, "bn")) g_tune.force_bn = value;
   else if (!strcmp(name, "swap_max_m")) g_tune.swap_max_m = value;
