@@ -363,6 +363,22 @@ def run_gpu(args):
     for i in range(args.warmup):
         step(i)
     barrier()
+    # Safety net: if a device-side wait of the owner form gave up during warm-up on any rank
+    # (status 401 / 402 / 403), say so in the line and measure the push form instead of
+    # publishing numbers computed on poisoned activations.
+    reduce_note = None
+    if world > 1:
+        code = torch.tensor([float(native.device_status())], device=device)
+        dist.all_reduce(code, op=dist.ReduceOp.MAX)
+        if code.item() != 0.0:
+            reduce_note = f"owner form gave up during warm-up (device status {int(code.item())})"
+            collective.poll_status()
+            for ws in list(collective._workspaces.values()):
+                ws.reset()
+            owner = False
+            for i in range(args.warmup):
+                step(i)
+            barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -581,6 +597,7 @@ def run_gpu(args):
             "config": {"workload": "MXFP8 dense decoder MLP block, hidden 2560, intermediate 9728",
                        "tokens": m, "parallelism": f"tp{world}", "soak_steps": soak_steps,
                        "reduce": "owner form" if owner else ("push form" if world > 1 else "none"),
+                       "reduce_note": reduce_note,
                        "step_outputs": outputs,
                        "l2": f"rotates {NUM_WEIGHT_SETS} weight sets "
                              f"({NUM_WEIGHT_SETS * sets[0].nbytes() * world / 1e6:.0f} MB > 126 MB L2)"},
