@@ -744,10 +744,69 @@ def run_tp_suite(group, world, rank, device, peaks):
     return out
 
 
+def run_ar_local(args, device):
+    """The owner-form reduce with all ranks of a 4-way group on ONE device (a single cooperative
+    grid, "peer" pointers local): the kernel a profiler can capture without a multi-rank run."""
+    import ctypes
+    from mach_b200 import native
+    lib, world, h, m = native.lib(), 4, HIDDEN, args.tokens
+    nbytes = lib.mach_ar_buffer_bytes(world, m, h)
+    buffers = []
+    for _ in range(world):
+        ptr = ctypes.c_void_p()
+        native._check(lib.mach_ar_buffer_alloc(nbytes, ctypes.byref(ptr)), "ar_buffer_alloc")
+        buffers.append(ptr.value)
+    arr = (ctypes.c_void_p * world)(*buffers)
+    handles = []
+    for r in range(world):
+        ws = ctypes.c_void_p()
+        native._check(lib.mach_ar_create(world, r, m, h, arr, ctypes.byref(ws)), "ar_create")
+        handles.append(ws.value)
+    g = torch.Generator(device=device).manual_seed(3)
+    rpo = (m + world - 1) // world
+    partials = [torch.randn(m, h, generator=g, device=device).to(torch.bfloat16) for _ in range(world)]
+    residual = torch.randn(m, h, generator=g, device=device).to(torch.bfloat16)
+    gamma = (0.1 * torch.randn(h, generator=g, device=device)).to(torch.bfloat16)
+    rows = [residual[r * rpo:min(m, (r + 1) * rpo)].contiguous() for r in range(world)]
+    norms = [torch.empty_like(t) for t in rows]
+    ress = [torch.empty_like(t) for t in rows]
+    codes = [torch.empty((m, h), dtype=torch.uint8, device=device) for _ in range(world)]
+    scales = [torch.empty(native.sf_bytes(m, h), dtype=torch.uint8, device=device) for _ in range(world)]
+
+    def ptrs(ts):
+        return (ctypes.c_void_p * world)(*[t.data_ptr() for t in ts])
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def launch():
+        native._check(lib.mach_allreduce_local_ranks(
+            world, (ctypes.c_void_p * world)(*handles), ptrs(partials), ptrs(rows), gamma.data_ptr(),
+            EPS, 1.0, ptrs(norms), ptrs(ress), ptrs(codes), ptrs(scales), m, h, 0, 1, stream),
+            "allreduce_local_ranks")
+    for _ in range(args.warmup):
+        launch()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        launch()
+    e1.record()
+    torch.cuda.synchronize()
+    print(json.dumps({"kernel_only": "ar_owner_local", "ranks_on_one_device": world, "tokens": m,
+                      "hidden": h, "us_per_launch": e0.elapsed_time(e1) * 1e3 / args.steps,
+                      "device_status": native.device_status()}))
+    for hnd in handles:
+        lib.mach_ar_destroy(hnd)
+    for b in buffers:
+        lib.mach_ar_buffer_free(b)
+
+
 def run_kernel_only(args, xs, sets, device):
     """One kernel of the step alone (for profiler captures and tile sweeps): `warmup` + `steps`
     launches cycling the weight sets, CUDA-event time of the `steps` launches on one JSON line."""
     from mach_b200 import native
+    if args.kernel_only == "ar_owner_local":
+        run_ar_local(args, device)
+        return
     m = args.tokens
     codes, scales = native.quantize_mxfp8(xs[0])
     inter_local = sets[0].w_down.shape[1]
@@ -1057,7 +1116,8 @@ def main():
                          "line per case, instead of the headline step")
     ap.add_argument("--soak", type=float, default=SOAK_SECONDS,
                     help="seconds of untimed steps before the timed region (clock samples)")
-    ap.add_argument("--kernel-only", choices=["gate_up_swiglu", "down", "quantize"], default=None,
+    ap.add_argument("--kernel-only", choices=["gate_up_swiglu", "down", "quantize", "ar_owner_local"],
+                    default=None,
                     help="run one kernel of the step alone (profiler captures)")
     args = ap.parse_args()
     if args.warmup < 3:

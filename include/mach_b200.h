@@ -358,6 +358,22 @@ MACH_API int mach_moe_combine(const void* y_bf16, const void* topk_weights_f32,
                               const void* pos_of, void* out_bf16, int64_t m, int64_t h,
                               int64_t topk, void* stream);
 
+/* Small-batch schedule of the whole layer (M <= 8 tokens, topk <= 16): three launches (quantise
+ * + expert map, W1 + SwiGLU + requant, W2 + weighted reduce) on the CUDA cores instead of the
+ * permutation and the grouped tensor-core GEMMs; same rounding points, the dot products summed
+ * in a different order. Replaces the reference's decode schedules (src/vllm_mach/mxfp6/moe.py:
+ * 74-88,126-188). Weights in the kernel layout of mach_moe_grouped_gemm (W1 stacked with
+ * gate/up rows interleaved by 32, swizzled scales packed over the stack). `scratch`:
+ * mach_moe_small_scratch_bytes bytes, caller-owned, contents undefined afterwards. */
+MACH_API size_t mach_moe_small_scratch_bytes(int64_t tokens, int64_t topk, int64_t hidden,
+                                             int64_t inter);
+MACH_API int mach_moe_small_batch(const void* hidden_bf16, const void* topk_weights_f32,
+                                  const void* topk_ids_i32, const void* expert_map_i32,
+                                  const void* w13, const void* s13, const void* w2, const void* s2,
+                                  void* scratch, void* out_bf16, int64_t m, int64_t topk,
+                                  int64_t experts, int64_t hidden, int64_t inter, int w_format,
+                                  void* stream);
+
 /* Staged form of the layer, for callers that drive the stages themselves the way the
  * reference's shims do (mxfp6_sm120_route / _grouped_gemm / _silu_grouped_gemm / _reduce,
  * src/vllm_mach/mxfp6/moe_utils.py:205-488). The activation arrives already quantised:

@@ -98,6 +98,40 @@ def _worker(rank, world, port, results):
                     failures.append(tag + " codes differ")
                 if not torch.equal(ora.unswizzle_scales(scales.cpu(), m, h), rs):
                     failures.append(tag + " scales differ")
+        # The always-correct route (NCCL all_reduce + the rounded-sum norm kernel): taken for a
+        # hidden size the fused kernel does not serve, and after a workspace is marked failed.
+        for h, mark_failed in ((8320, False), (2560, True)):
+            gamma = randn_bf16(1, h, 3, 0.1)[0].contiguous()
+            m = 40
+            partials = [randn_bf16(m, h, 4000 + r + h) for r in range(world)]
+            residual = randn_bf16(m, h, 4999)
+            if mark_failed:
+                for ws in collective._workspaces.values():
+                    ws.failed = True
+            try:
+                norm, res, codes, scales = collective.allreduce_add_rmsnorm(
+                    partials[rank].cuda(), residual.cuda(), gamma.cuda(), eps, group, want_quant=True)
+                first, count = collective.owner_rows(m, group)
+                o_codes, o_scales, o_res, o_norm = collective.allreduce_owner_add_rmsnorm(
+                    partials[rank].cuda(), residual[first:first + count].contiguous().cuda(),
+                    gamma.cuda(), eps, group, m)
+            finally:
+                for ws in collective._workspaces.values():
+                    ws.failed = False
+            torch.cuda.synchronize()
+            ref_norm, ref_res = ora.allreduce_rmsnorm(partials, residual, gamma, eps)
+            tag = f"nccl route h{h} rank{rank}"
+            # NCCL's summation order is its own: tolerance instead of bit equality
+            if float((norm.float().cpu() - ref_norm.float()).norm() / ref_norm.float().norm()) > 5e-3:
+                failures.append(tag + " norm differs")
+            if float((res.float().cpu() - ref_res.float()).norm() / ref_res.float().norm()) > 5e-3:
+                failures.append(tag + " residual differs")
+            rc, rs = ora.quantize_mxfp8(norm.cpu())
+            if not torch.equal(codes.view(torch.uint8).cpu(), rc):
+                failures.append(tag + " codes differ from the quantiser on its own norm")
+            if not torch.equal(o_res.cpu(), res[first:first + count].cpu()) or \
+                    not torch.equal(o_codes.view(torch.uint8).cpu(), codes.view(torch.uint8).cpu()):
+                failures.append(tag + " owner-form fallback differs from the push-form fallback")
         # Reduce-scatter from the down projection's epilogue: same BF16 partial sums, same rank
         # order, so the whole block must equal the separate GEMM + all-reduce bit for bit.
         from mach_b200.mlp import MxMlpWeights, mlp_block

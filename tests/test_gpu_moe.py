@@ -151,3 +151,67 @@ def test_scatter_quantize_equals_gather_quantize(nat, m, experts, top_k, hidden)
     assert live.numel() == m * top_k
     assert torch.equal(outs[0][0][live], outs[1][0][live])
     assert torch.equal(outs[0][1][live], outs[1][1][live])
+
+
+@pytest.mark.parametrize("m,experts,hidden,inter,top_k,fmt,ep", [
+    (1, 16, 256, 128, 4, "e4m3", None), (1, 256, 2048, 512, 8, "e2m3", None),
+    (2, 8, 512, 256, 2, "e3m2", None), (4, 32, 2048, 512, 8, "e2m3", (1, 2)),
+    (8, 16, 384, 192, 4, "e2m3", None), (8, 64, 256, 128, 8, "e4m3", (3, 4)),
+])
+def test_small_batch_schedule(nat, m, experts, hidden, inter, top_k, fmt, ep):
+    """The decode schedule (mach_moe_small_batch, M <= 8) against the oracle and against the
+    grouped tensor-core path on the same inputs. Same rounding points, another summation
+    order inside the dot products: the layer's tolerance applies (rtol = atol = 0.03)."""
+    from mach_b200 import moe
+    x = randn_bf16(m, hidden, 8400 + m)
+    logits = randn_bf16(m, experts, 8401 + m)
+    (c13, s13, c2, s2), w13_deq, w2_deq = make_experts(min(experts, 16), hidden, inter, 8402 + m, fmt)
+    base = c13.shape[0]
+    pick = [e % base for e in range(experts)]          # bounded CPU work: experts repeat modulo 16
+    shift = torch.tensor([(e // base) % 3 for e in range(experts)], dtype=torch.uint8)
+    c13, c2 = c13[pick], c2[pick]
+    s13 = s13[pick] + shift[:, None, None]
+    s2 = s2[pick] + shift[:, None, None]
+    d13 = lambda e: w13_deq(e % base) * 2.0 ** int(shift[e])
+    d2 = lambda e: w2_deq(e % base) * 2.0 ** int(shift[e])
+    topk_w, topk_ids = moe.router_topk(logits.cuda(), top_k)
+    expert_map, sel = None, list(range(experts))
+    if ep is not None:
+        rank, world = ep
+        per = experts // world
+        sel = list(range(rank * per, (rank + 1) * per))
+        expert_map = torch.full((experts,), -1, dtype=torch.int32)
+        expert_map[rank * per:(rank + 1) * per] = torch.arange(per, dtype=torch.int32)
+    weights = moe.MoeWeights.from_logical(c13[sel].cuda(), s13[sel].cuda(), c2[sel].cuda(),
+                                          s2[sel].cuda(), fmt)
+    emap = None if expert_map is None else expert_map.cuda()
+    assert m <= moe.SMALL_BATCH_MAX_TOKENS
+    small = moe.experts_forward(x.cuda(), weights, topk_w, topk_ids, emap)
+    limit = moe.SMALL_BATCH_MAX_TOKENS
+    moe.SMALL_BATCH_MAX_TOKENS = 0
+    try:
+        grouped = moe.experts_forward(x.cuda(), weights, topk_w, topk_ids, emap)
+    finally:
+        moe.SMALL_BATCH_MAX_TOKENS = limit
+    torch.cuda.synchronize()
+    assert nat.device_status() == 0
+    ref = ora.moe_forward(x, lambda e: d13(sel[e]), lambda e: d2(sel[e]), topk_w.cpu(),
+                          topk_ids.cpu(), expert_map)
+    assert torch.isfinite(small.float()).all()
+    assert torch.allclose(small.float().cpu(), ref.float(), rtol=0.03, atol=0.03), \
+        float((small.float().cpu() - ref.float()).abs().max())
+    assert torch.allclose(small.float(), grouped.float(), rtol=0.03, atol=0.03)
+    assert rel_fro(small, ref) <= 1e-2
+
+
+def test_small_batch_refuses_what_it_does_not_implement(nat):
+    import ctypes
+    lib = nat.lib()
+    d = torch.zeros(64, dtype=torch.uint8, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    args = [d.data_ptr()] * 10
+    assert lib.mach_moe_small_batch(*args, 9, 8, 256, 2048, 512, 3, stream) == 2      # M > 8
+    assert lib.mach_moe_small_batch(*args, 1, 8, 256, 2000, 512, 3, stream) == 2      # hidden % 128
+    assert lib.mach_moe_small_batch(*args, 1, 8, 256, 2048, 512, 7, stream) == 1      # format
+    assert lib.mach_moe_small_batch(*args, 0, 8, 256, 2048, 512, 3, stream) == 0      # empty batch
+    assert lib.mach_moe_small_scratch_bytes(1, 8, 2048, 512) == 2048 * 4 + 8 * 512 * 4 + 8 * 4

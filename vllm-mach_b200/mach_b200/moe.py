@@ -58,6 +58,12 @@ def router_topk(logits: torch.Tensor, top_k: int):
     return w, ids
 
 
+# Largest batch that takes the small-batch schedule (three CUDA-core launches; see
+# mach_moe_small_batch). Measured on B200, 256 experts / top-8 / hidden 2048 / intermediate 512:
+# the cross-over with the grouped tensor-core path lies above 8 tokens.
+SMALL_BATCH_MAX_TOKENS = 8
+
+
 def chunk_rows_for(tokens: int, top_k: int, experts: int) -> int:
     if tokens <= 16:
         return 16
@@ -86,6 +92,17 @@ def experts_forward(hidden, weights: MoeWeights, topk_weights, topk_ids, expert_
         return out
     lib, dev = native.lib(), hidden.device
     e = weights.experts
+    if m <= SMALL_BATCH_MAX_TOKENS and top_k <= 16:
+        nbytes = int(lib.mach_moe_small_scratch_bytes(m, top_k, h, weights.inter))
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            native._check(lib.mach_moe_small_batch(
+                native._ptr(hidden), native._ptr(topk_weights), native._ptr(topk_ids),
+                native._ptr(expert_map), native._ptr(weights.w13), native._ptr(weights.s13),
+                native._ptr(weights.w2), native._ptr(weights.s2), native._ptr(scratch),
+                native._ptr(out), m, top_k, e, h, weights.inter, native._FORMATS[weights.fmt],
+                native._stream(hidden)), "moe_small_batch")
+        return out
     chunk = chunk_rows_for(m, top_k, e)
     rows_cap = int(lib.mach_moe_rows_cap(m, top_k, e))
     work_cap = int(lib.mach_moe_work_cap(m, top_k, e, chunk))

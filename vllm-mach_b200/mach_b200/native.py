@@ -74,6 +74,9 @@ _SIGNATURES = {
     "mach_moe_grouped_gemm": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64,
                                      _I64, _INT, _INT, _P]),
     "mach_moe_combine": (_INT, [_P, _P, _P, _P, _I64, _I64, _I64, _P]),
+    "mach_moe_small_scratch_bytes": (ctypes.c_size_t, [_I64, _I64, _I64, _I64]),
+    "mach_moe_small_batch": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64,
+                                    _I64, _INT, _P]),
     "mach_moe_scatter_codes": (_INT, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P]),
     "mach_moe_stage_offsets": (_INT, [_P, _P, _I64, _P, _P, _P]),
     "mach_moe_work_from_offsets": (_INT, [_P, _P, _I64, _I64, _I64, _P, _P, _P]),
