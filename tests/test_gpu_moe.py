@@ -156,7 +156,7 @@ def test_scatter_quantize_equals_gather_quantize(nat, m, experts, top_k, hidden)
 @pytest.mark.parametrize("m,experts,hidden,inter,top_k,fmt,ep", [
     (1, 16, 256, 128, 4, "e4m3", None), (1, 256, 2048, 512, 8, "e2m3", None),
     (2, 8, 512, 256, 2, "e3m2", None), (4, 32, 2048, 512, 8, "e2m3", (1, 2)),
-    (8, 16, 384, 192, 4, "e2m3", None), (8, 64, 256, 128, 8, "e4m3", (3, 4)),
+    (8, 16, 384, 256, 4, "e2m3", None), (8, 64, 256, 128, 8, "e4m3", (3, 4)),
 ])
 def test_small_batch_schedule(nat, m, experts, hidden, inter, top_k, fmt, ep):
     """The decode schedule (mach_moe_small_batch, M <= 8) against the oracle and against the

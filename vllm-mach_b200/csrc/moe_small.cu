@@ -46,29 +46,45 @@ __device__ __forceinline__ float decode_weight(uint32_t code, int fmt) {
   return (code & 0x20u) ? -mag : mag;
 }
 
-// 16 consecutive weights of one row (unit u covers K indices [16u, 16u + 16)) times 16 activation
-// values; the weights' common E8M0 scale (32-element groups: two units per group) is applied by
-// the caller. lut: decoded code values in shared memory.
-__device__ __forceinline__ float dot16(const uint8_t* __restrict__ row, int unit, int fmt,
-                                       const float* __restrict__ lut, const float* __restrict__ act) {
-  float acc = 0.0f;
+// One unit = 16 consecutive K indices of one weight row: 16 bytes (E4M3) or 12 bytes (6-bit).
+struct WeightUnit {
+  uint32_t w[4];
+};
+__device__ __forceinline__ WeightUnit load_unit(const uint8_t* __restrict__ row, int unit, int fmt) {
+  WeightUnit u;
   if (fmt == MACH_FMT_E4M3) {
     const uint4 v = __ldg(reinterpret_cast<const uint4*>(row + (size_t)unit * 16));
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-      acc = __fmaf_rn(lut[(w[i >> 2] >> (8 * (i & 3))) & 0xFFu], act[i], acc);
+    u.w[0] = v.x; u.w[1] = v.y; u.w[2] = v.z; u.w[3] = v.w;
   } else {
     const uint32_t* p = reinterpret_cast<const uint32_t*>(row + (size_t)unit * 12);
     const uint32_t a = __ldg(p), b = __ldg(p + 1), c = __ldg(p + 2);
     // four 24-bit words, element i of a word in bits [6i, 6i + 6)
-    const uint32_t word[4] = {a & 0xFFFFFFu, (a >> 24) | ((b & 0xFFFFu) << 8),
-                              (b >> 16) | ((c & 0xFFu) << 16), c >> 8};
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-      acc = __fmaf_rn(lut[(word[i >> 2] >> (6 * (i & 3))) & 0x3Fu], act[i], acc);
+    u.w[0] = a & 0xFFFFFFu;
+    u.w[1] = (a >> 24) | ((b & 0xFFFFu) << 8);
+    u.w[2] = (b >> 16) | ((c & 0xFFu) << 16);
+    u.w[3] = c >> 8;
   }
+  return u;
+}
+// Dot product of a unit with its 16 activation values; the unit's E8M0 scale (32-element
+// groups: two units per group) is applied by the caller. lut: decoded code values in shared
+// memory. The activations sit in shared memory TRANSPOSED, element j of unit u at
+// act_t[j * units + u], so the lanes of a warp (consecutive units) read consecutive words.
+__device__ __forceinline__ float dot16(const WeightUnit& u, int fmt, const float* __restrict__ lut,
+                                       const float* __restrict__ act_t, int units, int unit) {
+  float acc = 0.0f;
+  const int bits = fmt == MACH_FMT_E4M3 ? 8 : 6;
+  const uint32_t mask = fmt == MACH_FMT_E4M3 ? 0xFFu : 0x3Fu;
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    acc = __fmaf_rn(lut[(u.w[i >> 2] >> ((i & 3) * bits)) & mask], act_t[i * units + unit], acc);
   return acc;
+}
+// Copies one activation row (n floats, n % 16 == 0) from global memory into the transposed
+// shared layout above; all threads of the CTA.
+__device__ __forceinline__ void stage_transposed(float* act_t, const float* __restrict__ row, int n) {
+  const int units = n >> 4;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) act_t[(i & 15) * units + (i >> 4)] = __ldg(row + i);
 }
 
 __device__ __forceinline__ void load_lut(float* lut, int fmt) {
@@ -127,44 +143,62 @@ moe_small_front_kernel(const __nv_bfloat16* __restrict__ hidden, const int* __re
 }
 
 // ---- w1: one CTA per (pair, 32 output features); warp w computes feature 32 * block + w:
-// its gate row and its up row of the expert's gate/up-interleaved W1.
+// its gate row and its up row of the expert's gate/up-interleaved W1. Dynamic shared memory:
+// the token's dequantised activation row, k floats.
 __global__ void __launch_bounds__(1024)
 moe_small_w1_kernel(const float* __restrict__ act, const int* __restrict__ pair_expert,
                     const uint8_t* __restrict__ w13, const uint8_t* __restrict__ s13, int topk,
                     int k, int inter, int fmt, int row_bytes, float* __restrict__ h_deq) {
+  extern __shared__ float act_t[];
   __shared__ float lut[256];
   __shared__ float vals[32];
   pdl_launch_dependents();
   load_lut(lut, fmt);
-  pdl_wait();
   const int pair = blockIdx.y;
-  const int e = pair_expert[pair];
-  if (e < 0) return;  // block-uniform
-  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int feat = blockIdx.x * 32 + warp;                 // < inter (inter % 32 == 0)
   const int token = pair / topk;
   const int k_tiles = (k + 127) >> 7;
+  const int units = k >> 4;
+  pdl_wait();
+  const int e = pair_expert[pair];
+  if (e < 0) return;  // block-uniform
   // physical rows inside the stacked, interleaved W1: gate feature f at 64 * (f / 32) + f % 32
   const int64_t g_row = (int64_t)e * 2 * inter + 64 * (feat >> 5) + (feat & 31);
   const int64_t u_row = g_row + 32;
   const uint8_t* g_ptr = w13 + g_row * row_bytes;
   const uint8_t* u_ptr = w13 + u_row * row_bytes;
-  const float* a_row = act + (size_t)token * k;
-  float gate = 0.0f, up = 0.0f;
-  for (int unit = lane; unit < (k >> 4); unit += 32) {
-    float a[16];
-    const float4* ap = reinterpret_cast<const float4*>(a_row + unit * 16);
+  // the first pass's weights go out before the activation row is staged
+  WeightUnit gw[4], uw[4];
+  float gs[4], us[4];
+  auto fetch = [&](int base) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float4 t = __ldg(ap + i);
-      a[4 * i] = t.x; a[4 * i + 1] = t.y; a[4 * i + 2] = t.z; a[4 * i + 3] = t.w;
+      const int unit = base + 32 * i + lane;
+      if (unit < units) {
+        gw[i] = load_unit(g_ptr, unit, fmt);
+        uw[i] = load_unit(u_ptr, unit, fmt);
+        gs[i] = pow2_of_byte(__ldg(s13 + sf_offset((int)g_row, unit >> 1, k_tiles)));
+        us[i] = pow2_of_byte(__ldg(s13 + sf_offset((int)u_row, unit >> 1, k_tiles)));
+      }
     }
-    const int group = unit >> 1;
-    const float gs = pow2_of_byte(__ldg(s13 + sf_offset((int)g_row, group, k_tiles)));
-    const float us = pow2_of_byte(__ldg(s13 + sf_offset((int)u_row, group, k_tiles)));
-    gate = __fmaf_rn(dot16(g_ptr, unit, fmt, lut, a), gs, gate);
-    up = __fmaf_rn(dot16(u_ptr, unit, fmt, lut, a), us, up);
+  };
+  fetch(0);
+  stage_transposed(act_t, act + (size_t)token * k, k);
+  __syncthreads();
+  float gate = 0.0f, up = 0.0f;
+  // Four units per lane and pass (2048 K indices per warp), all loads of a pass in flight
+  // together: one memory round trip per pass.
+  for (int base = 0; base < units; base += 128) {
+    if (base > 0) fetch(base);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int unit = base + 32 * i + lane;
+      if (unit < units) {
+        gate = __fmaf_rn(dot16(gw[i], fmt, lut, act_t, units, unit), gs[i], gate);
+        up = __fmaf_rn(dot16(uw[i], fmt, lut, act_t, units, unit), us[i], up);
+      }
+    }
   }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) {
@@ -185,47 +219,80 @@ moe_small_w1_kernel(const float* __restrict__ act, const int* __restrict__ pair_
   }
 }
 
-// ---- w2: one warp per (token, output feature); the top-k pairs of the token in k order.
+// ---- w2: one CTA per (token, group of features); warp (f, j) computes y = bf16(dot) of feature
+// f with the token's j-th pair, all pairs of a feature at the same time; then one thread per
+// feature folds them in k order: acc = fma(w_k, y_k, acc). Dynamic shared memory: the
+// dequantised SwiGLU rows of the token's pairs, topk_pad x inter floats.
 __global__ void __launch_bounds__(1024)
 moe_small_w2_kernel(const float* __restrict__ h_deq, const int* __restrict__ pair_expert,
                     const float* __restrict__ topk_weights, const uint8_t* __restrict__ w2,
-                    const uint8_t* __restrict__ s2, int topk, int hidden, int inter, int fmt,
-                    int row_bytes, __nv_bfloat16* __restrict__ out) {
+                    const uint8_t* __restrict__ s2, int topk, int topk_pad, int hidden, int inter,
+                    int fmt, int row_bytes, __nv_bfloat16* __restrict__ out) {
+  extern __shared__ float h_t[];
   __shared__ float lut[256];
+  __shared__ float ys[32];
   pdl_launch_dependents();
   load_lut(lut, fmt);
-  pdl_wait();
-  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int feats = 32 / topk_pad;             // features per CTA
+  const int f_local = warp / topk_pad;
+  const int j = warp - f_local * topk_pad;
   const int token = blockIdx.y;
-  const int feat = blockIdx.x * 32 + warp;
-  if (feat >= hidden) return;
+  const int feat = blockIdx.x * feats + f_local;
   const int k_tiles = (inter + 127) >> 7;
-  float acc = 0.0f;
-  for (int j = 0; j < topk; ++j) {
-    const int pair = token * topk + j;
-    const int e = pair_expert[pair];
-    if (e < 0) continue;  // warp-uniform
-    const int64_t row = (int64_t)e * hidden + feat;
-    const uint8_t* r_ptr = w2 + row * row_bytes;
-    const float* h_row = h_deq + (size_t)pair * inter;
+  const int units = inter >> 4;
+  pdl_wait();
+  const int pair = token * topk + j;
+  const int e = (j < topk && feat < hidden) ? pair_expert[pair] : -1;  // warp-uniform
+  const int64_t row = (int64_t)max(e, 0) * hidden + feat;
+  const uint8_t* r_ptr = w2 + row * row_bytes;
+  WeightUnit w[4];
+  float ws[4];
+  auto fetch = [&](int base) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int unit = base + 32 * i + lane;
+      if (e >= 0 && unit < units) {
+        w[i] = load_unit(r_ptr, unit, fmt);
+        ws[i] = pow2_of_byte(__ldg(s2 + sf_offset((int)row, unit >> 1, k_tiles)));
+      }
+    }
+  };
+  fetch(0);
+  for (int q = 0; q < topk; ++q)
+    if (pair_expert[token * topk + q] >= 0)   // block-uniform
+      stage_transposed(h_t + (size_t)q * inter, h_deq + (size_t)(token * topk + q) * inter, inter);
+  __syncthreads();
+  float y = 0.0f;
+  if (e >= 0) {
+    const float* mine = h_t + (size_t)j * inter;
     float dot = 0.0f;
-    for (int unit = lane; unit < (inter >> 4); unit += 32) {
-      float a[16];
-      const float4* ap = reinterpret_cast<const float4*>(h_row + unit * 16);
+    for (int base = 0; base < units; base += 128) {
+      if (base > 0) fetch(base);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float4 t = __ldg(ap + i);
-        a[4 * i] = t.x; a[4 * i + 1] = t.y; a[4 * i + 2] = t.z; a[4 * i + 3] = t.w;
+        const int unit = base + 32 * i + lane;
+        if (unit < units) dot = __fmaf_rn(dot16(w[i], fmt, lut, mine, units, unit), ws[i], dot);
       }
-      const float ws = pow2_of_byte(__ldg(s2 + sf_offset((int)row, unit >> 1, k_tiles)));
-      dot = __fmaf_rn(dot16(r_ptr, unit, fmt, lut, a), ws, dot);
     }
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) dot = __fadd_rn(dot, __shfl_xor_sync(0xffffffffu, dot, d));
-    acc = __fmaf_rn(topk_weights[pair], bf16_round(dot), acc);
+    y = bf16_round(dot);
   }
-  if (lane == 0) out[(size_t)token * hidden + feat] = __float2bfloat16_rn(acc);
+  if (lane == 0) ys[warp] = y;
+  __syncthreads();
+  if ((int)threadIdx.x < feats) {
+    const int f = blockIdx.x * feats + threadIdx.x;
+    if (f < hidden) {
+      float acc = 0.0f;
+      for (int q = 0; q < topk; ++q) {
+        const int pr = token * topk + q;
+        if (pair_expert[pr] < 0) continue;
+        acc = __fmaf_rn(topk_weights[pr], ys[threadIdx.x * topk_pad + q], acc);
+      }
+      out[(size_t)token * hidden + f] = __float2bfloat16_rn(acc);
+    }
+  }
 }
 
 int launched(cudaError_t e, const char* what) {
@@ -279,16 +346,24 @@ extern "C" int mach_moe_small_batch(const void* hidden_bf16, const void* topk_we
                               (int)topk, (int)hidden, act, pair_expert),
                     "moe_small_front");
   if (rc != MACH_OK) return rc;
+  if (hidden * 4 > 40 * 1024 || 16 * inter * 4 > 40 * 1024)
+    return fail(MACH_ERR_UNSUPPORTED, "moe_small_batch: hidden <= 10240, intermediate <= 640 required");
   rc = launched(launch_ex(moe_small_w1_kernel, dim3((unsigned)(inter / 32), (unsigned)(m * topk)),
-                          dim3(1024), 0, st, dim3(1, 1, 1), pdl_enabled(), (const float*)act,
+                          dim3(1024), (size_t)hidden * 4, st, dim3(1, 1, 1), pdl_enabled(),
+                          (const float*)act,
                           (const int*)pair_expert, (const uint8_t*)w13, (const uint8_t*)s13,
                           (int)topk, (int)hidden, (int)inter, w_format, row1, h_deq),
                 "moe_small_w1");
   if (rc != MACH_OK) return rc;
-  return launched(launch_ex(moe_small_w2_kernel, dim3((unsigned)((hidden + 31) / 32), (unsigned)m),
-                            dim3(1024), 0, st, dim3(1, 1, 1), pdl_enabled(), (const float*)h_deq,
+  int topk_pad = 1;
+  while (topk_pad < topk) topk_pad <<= 1;       // 1, 2, 4, 8, 16: divides the 32 warps of a CTA
+  const int feats = 32 / topk_pad;
+  return launched(launch_ex(moe_small_w2_kernel,
+                            dim3((unsigned)((hidden + feats - 1) / feats), (unsigned)m), dim3(1024),
+                            (size_t)topk_pad * inter * 4, st, dim3(1, 1, 1), pdl_enabled(),
+                            (const float*)h_deq,
                             (const int*)pair_expert, (const float*)topk_weights_f32,
-                            (const uint8_t*)w2, (const uint8_t*)s2, (int)topk, (int)hidden,
-                            (int)inter, w_format, row2, (__nv_bfloat16*)out_bf16),
+                            (const uint8_t*)w2, (const uint8_t*)s2, (int)topk, topk_pad,
+                            (int)hidden, (int)inter, w_format, row2, (__nv_bfloat16*)out_bf16),
                   "moe_small_w2");
 }

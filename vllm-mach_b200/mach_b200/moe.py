@@ -92,7 +92,7 @@ def experts_forward(hidden, weights: MoeWeights, topk_weights, topk_ids, expert_
         return out
     lib, dev = native.lib(), hidden.device
     e = weights.experts
-    if m <= SMALL_BATCH_MAX_TOKENS and top_k <= 16:
+    if m <= SMALL_BATCH_MAX_TOKENS and top_k <= 16 and h <= 10240 and weights.inter <= 640:
         nbytes = int(lib.mach_moe_small_scratch_bytes(m, top_k, h, weights.inter))
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         with torch.cuda.device(dev):
