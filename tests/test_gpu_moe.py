@@ -185,11 +185,11 @@ def test_small_batch_schedule(nat, m, experts, hidden, inter, top_k, fmt, ep):
     weights = moe.MoeWeights.from_logical(c13[sel].cuda(), s13[sel].cuda(), c2[sel].cuda(),
                                           s2[sel].cuda(), fmt)
     emap = None if expert_map is None else expert_map.cuda()
-    assert m <= moe.SMALL_BATCH_MAX_TOKENS
-    small = moe.experts_forward(x.cuda(), weights, topk_w, topk_ids, emap)
     limit = moe.SMALL_BATCH_MAX_TOKENS
-    moe.SMALL_BATCH_MAX_TOKENS = 0
     try:
+        moe.SMALL_BATCH_MAX_TOKENS = 8          # the entry point's own limit
+        small = moe.experts_forward(x.cuda(), weights, topk_w, topk_ids, emap)
+        moe.SMALL_BATCH_MAX_TOKENS = 0
         grouped = moe.experts_forward(x.cuda(), weights, topk_w, topk_ids, emap)
     finally:
         moe.SMALL_BATCH_MAX_TOKENS = limit

@@ -8,16 +8,17 @@
 // weights (gate/up-interleaved W1, swizzled E8M0 scales).
 //
 //   front:  x -> MXFP8 (the activation quantiser) -> dequantised FP32 row; expert_map applied
-//   w1:     per pair and 32 output features: gate/up dot products (FP32, weights decoded from
-//           E4M3 / 6-bit codes x 2^(scale-127)), BF16, SwiGLU (bf16(bf16(silu(g)) * u)), MXFP8
-//           requant of the 32 values -> dequantised FP32 (what the down projection multiplies)
-//   w2:     per token and output feature: for k ascending y_k = bf16(dot), acc = fma(w_k, y_k, acc)
+//   w1:     per pair and output feature: gate/up dot products (FP32, weights decoded from E4M3 /
+//           6-bit codes x 2^(scale-127)), BF16, SwiGLU v = bf16(bf16(silu(g)) * u)
+//   w2:     per token and output feature: the MXFP8 requant of v (blocks of 32, on load), then
+//           for k ascending y_k = bf16(dot), acc = fma(w_k, y_k, acc)
 //
 // Rounding points are those of the large-batch path (quantise, BF16 between the stages, FP32
 // combine); only the summation order inside a dot product differs (lane-strided + shuffle tree
 // instead of the tensor core's), which the layer's tolerance (rtol = atol = 0.03,
 // tests/native_mxfp6/test_moe.py:248 of the reference) covers.
 #include <cuda_bf16.h>
+#include <cuda_fp6.h>
 #include <cuda_fp8.h>
 #include "host_util.h"
 #include "ptx.cuh"
@@ -34,31 +35,20 @@ __device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
   return __half2float(*reinterpret_cast<const __half*>(&h));
 }
 
-// Value of a weight code: E4M3 byte, or a 6-bit code (sign, 2/3 exponent bits, 3/2 mantissa bits).
-__device__ __forceinline__ float decode_weight(uint32_t code, int fmt) {
-  if (fmt == MACH_FMT_E4M3) return e4m3_to_float(code);
-  const int mbits = fmt == MACH_FMT_E2M3 ? 3 : 2;
-  const int bias = fmt == MACH_FMT_E2M3 ? 1 : 3;
-  const uint32_t e = (code >> mbits) & ((1u << (5 - mbits)) - 1u);
-  const uint32_t man = code & ((1u << mbits) - 1u);
-  const float frac = (float)man / (float)(1u << mbits);
-  const float mag = e == 0 ? frac * exp2f((float)(1 - bias)) : (1.0f + frac) * exp2f((float)((int)e - bias));
-  return (code & 0x20u) ? -mag : mag;
-}
-
-// One unit = 16 consecutive K indices of one weight row: 16 bytes (E4M3) or 12 bytes (6-bit).
+// One unit = 16 consecutive K indices of one weight row: 16 bytes (E4M3) or 12 bytes (6-bit,
+// four 24-bit words with element i of a word in bits [6i, 6i + 6)).
 struct WeightUnit {
   uint32_t w[4];
 };
-__device__ __forceinline__ WeightUnit load_unit(const uint8_t* __restrict__ row, int unit, int fmt) {
+template <int kFmt>
+__device__ __forceinline__ WeightUnit load_unit(const uint8_t* __restrict__ row, int unit) {
   WeightUnit u;
-  if (fmt == MACH_FMT_E4M3) {
+  if (kFmt == MACH_FMT_E4M3) {
     const uint4 v = __ldg(reinterpret_cast<const uint4*>(row + (size_t)unit * 16));
     u.w[0] = v.x; u.w[1] = v.y; u.w[2] = v.z; u.w[3] = v.w;
   } else {
     const uint32_t* p = reinterpret_cast<const uint32_t*>(row + (size_t)unit * 12);
     const uint32_t a = __ldg(p), b = __ldg(p + 1), c = __ldg(p + 2);
-    // four 24-bit words, element i of a word in bits [6i, 6i + 6)
     u.w[0] = a & 0xFFFFFFu;
     u.w[1] = (a >> 24) | ((b & 0xFFFFu) << 8);
     u.w[2] = (b >> 16) | ((c & 0xFFu) << 16);
@@ -66,30 +56,48 @@ __device__ __forceinline__ WeightUnit load_unit(const uint8_t* __restrict__ row,
   }
   return u;
 }
-// Dot product of a unit with its 16 activation values; the unit's E8M0 scale (32-element
-// groups: two units per group) is applied by the caller. lut: decoded code values in shared
-// memory. The activations sit in shared memory TRANSPOSED, element j of unit u at
-// act_t[j * units + u], so the lanes of a warp (consecutive units) read consecutive words.
-__device__ __forceinline__ float dot16(const WeightUnit& u, int fmt, const float* __restrict__ lut,
-                                       const float* __restrict__ act_t, int units, int unit) {
+// Two codes -> two FP32 values with the hardware conversions (cvt.rn.f16x2.{e4m3x2, e2m3x2,
+// e3m2x2}; every code value is exact in FP16).
+template <int kFmt>
+__device__ __forceinline__ float2 decode2(uint32_t pair16) {
+  __half2_raw h;
+  if (kFmt == MACH_FMT_E4M3)
+    h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(pair16), __NV_E4M3);
+  else
+    h = __nv_cvt_fp6x2_to_halfraw2(static_cast<__nv_fp6x2_storage_t>(pair16),
+                                   kFmt == MACH_FMT_E2M3 ? __NV_E2M3 : __NV_E3M2);
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+// Dot product of a unit with its 16 activation values (registers); the unit's E8M0 scale
+// (32-element groups: two units per group) is applied by the caller.
+template <int kFmt>
+__device__ __forceinline__ float dot16(const WeightUnit& u, const float (&act)[16]) {
   float acc = 0.0f;
-  const int bits = fmt == MACH_FMT_E4M3 ? 8 : 6;
-  const uint32_t mask = fmt == MACH_FMT_E4M3 ? 0xFFu : 0x3Fu;
 #pragma unroll
-  for (int i = 0; i < 16; ++i)
-    acc = __fmaf_rn(lut[(u.w[i >> 2] >> ((i & 3) * bits)) & mask], act_t[i * units + unit], acc);
+  for (int i = 0; i < 4; ++i) {
+    uint32_t lo, hi;  // codes (0, 1) and (2, 3) of word i, one code per byte
+    if (kFmt == MACH_FMT_E4M3) {
+      lo = u.w[i] & 0xFFFFu;
+      hi = u.w[i] >> 16;
+    } else {
+      lo = (u.w[i] & 0x3Fu) | ((u.w[i] << 2) & 0x3F00u);
+      hi = ((u.w[i] >> 12) & 0x3Fu) | ((u.w[i] >> 10) & 0x3F00u);
+    }
+    const float2 a = decode2<kFmt>(lo), b = decode2<kFmt>(hi);
+    acc = __fmaf_rn(a.x, act[4 * i], acc);
+    acc = __fmaf_rn(a.y, act[4 * i + 1], acc);
+    acc = __fmaf_rn(b.x, act[4 * i + 2], acc);
+    acc = __fmaf_rn(b.y, act[4 * i + 3], acc);
+  }
   return acc;
 }
-// Copies one activation row (n floats, n % 16 == 0) from global memory into the transposed
-// shared layout above; all threads of the CTA.
-__device__ __forceinline__ void stage_transposed(float* act_t, const float* __restrict__ row, int n) {
-  const int units = n >> 4;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) act_t[(i & 15) * units + (i >> 4)] = __ldg(row + i);
-}
-
-__device__ __forceinline__ void load_lut(float* lut, int fmt) {
-  const int entries = fmt == MACH_FMT_E4M3 ? 256 : 64;
-  for (int i = threadIdx.x; i < entries; i += blockDim.x) lut[i] = decode_weight((uint32_t)i, fmt);
+__device__ __forceinline__ void load_act16(const float* __restrict__ p, float (&act)[16]) {
+  const float4* v = reinterpret_cast<const float4*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 t = __ldg(v + i);
+    act[4 * i] = t.x; act[4 * i + 1] = t.y; act[4 * i + 2] = t.z; act[4 * i + 3] = t.w;
+  }
 }
 
 __device__ __forceinline__ float pow2_of_byte(uint32_t byte) {
@@ -142,61 +150,53 @@ moe_small_front_kernel(const __nv_bfloat16* __restrict__ hidden, const int* __re
   }
 }
 
-// ---- w1: one CTA per (pair, 32 output features); warp w computes feature 32 * block + w:
-// its gate row and its up row of the expert's gate/up-interleaved W1. Dynamic shared memory:
-// the token's dequantised activation row, k floats.
-__global__ void __launch_bounds__(1024)
+// ---- w1: one warp per (pair, output feature): the gate row and the up row of the feature in
+// the expert's gate/up-interleaved W1, both rows' loads in flight together. A lane keeps its
+// slice of the token's activation row in registers (up to four units = 64 values: K <= 2048
+// per pass). Writes v = bf16(bf16(silu(gate)) * up) as FP32; the MXFP8 requant of v (blocks of
+// 32 features) happens where the down projection loads it.
+template <int kFmt>
+__global__ void __launch_bounds__(128)
 moe_small_w1_kernel(const float* __restrict__ act, const int* __restrict__ pair_expert,
                     const uint8_t* __restrict__ w13, const uint8_t* __restrict__ s13, int topk,
-                    int k, int inter, int fmt, int row_bytes, float* __restrict__ h_deq) {
-  extern __shared__ float act_t[];
-  __shared__ float lut[256];
-  __shared__ float vals[32];
+                    int k, int inter, int row_bytes, float* __restrict__ h_val) {
   pdl_launch_dependents();
-  load_lut(lut, fmt);
   const int pair = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int feat = blockIdx.x * 32 + warp;                 // < inter (inter % 32 == 0)
   const int token = pair / topk;
   const int k_tiles = (k + 127) >> 7;
   const int units = k >> 4;
+  const int feat = blockIdx.x * 4 + warp;
   pdl_wait();
   const int e = pair_expert[pair];
-  if (e < 0) return;  // block-uniform
+  if (e < 0 || feat >= inter) return;  // warp-uniform
   // physical rows inside the stacked, interleaved W1: gate feature f at 64 * (f / 32) + f % 32
   const int64_t g_row = (int64_t)e * 2 * inter + 64 * (feat >> 5) + (feat & 31);
   const int64_t u_row = g_row + 32;
   const uint8_t* g_ptr = w13 + g_row * row_bytes;
   const uint8_t* u_ptr = w13 + u_row * row_bytes;
-  // the first pass's weights go out before the activation row is staged
-  WeightUnit gw[4], uw[4];
-  float gs[4], us[4];
-  auto fetch = [&](int base) {
+  const float* a_row = act + (size_t)token * k;
+  float gate = 0.0f, up = 0.0f;
+  for (int base = 0; base < units; base += 128) {
+    WeightUnit gw[4], uw[4];
+    float gs[4], us[4];
+    float a[4][16];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int unit = base + 32 * i + lane;
       if (unit < units) {
-        gw[i] = load_unit(g_ptr, unit, fmt);
-        uw[i] = load_unit(u_ptr, unit, fmt);
+        gw[i] = load_unit<kFmt>(g_ptr, unit);
+        uw[i] = load_unit<kFmt>(u_ptr, unit);
         gs[i] = pow2_of_byte(__ldg(s13 + sf_offset((int)g_row, unit >> 1, k_tiles)));
         us[i] = pow2_of_byte(__ldg(s13 + sf_offset((int)u_row, unit >> 1, k_tiles)));
+        load_act16(a_row + unit * 16, a[i]);
       }
     }
-  };
-  fetch(0);
-  stage_transposed(act_t, act + (size_t)token * k, k);
-  __syncthreads();
-  float gate = 0.0f, up = 0.0f;
-  // Four units per lane and pass (2048 K indices per warp), all loads of a pass in flight
-  // together: one memory round trip per pass.
-  for (int base = 0; base < units; base += 128) {
-    if (base > 0) fetch(base);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int unit = base + 32 * i + lane;
-      if (unit < units) {
-        gate = __fmaf_rn(dot16(gw[i], fmt, lut, act_t, units, unit), gs[i], gate);
-        up = __fmaf_rn(dot16(uw[i], fmt, lut, act_t, units, unit), us[i], up);
+      if (base + 32 * i + lane < units) {
+        gate = __fmaf_rn(dot16<kFmt>(gw[i], a[i]), gs[i], gate);
+        up = __fmaf_rn(dot16<kFmt>(uw[i], a[i]), us[i], up);
       }
     }
   }
@@ -205,94 +205,86 @@ moe_small_w1_kernel(const float* __restrict__ act, const int* __restrict__ pair_
     gate = __fadd_rn(gate, __shfl_xor_sync(0xffffffffu, gate, d));
     up = __fadd_rn(up, __shfl_xor_sync(0xffffffffu, up, d));
   }
-  if (lane == 0) vals[warp] = swiglu_bf16(bf16_round(gate), bf16_round(up));
-  __syncthreads();
-  if (warp == 0) {
-    const float v = vals[lane];
-    float amax = fabsf(v);
+  if (lane == 0) h_val[(size_t)pair * inter + feat] = swiglu_bf16(bf16_round(gate), bf16_round(up));
+}
+
+// 16 SwiGLU values of a unit -> what the MXFP8 requant leaves of them: the block of 32 is this
+// lane's unit and the neighbouring lane's (units 2g and 2g + 1 sit in lanes that differ in bit
+// 0), so the block maximum is one shuffle away.
+__device__ __forceinline__ void requant16(float (&v)[16]) {
+  float amax = 0.0f;
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
-    const uint32_t bits = mx_scale_bits(amax);
-    const uint32_t q = e4m3x2(__fmul_rn(v, mx_inverse(bits)), 0.0f) & 0xFFu;
-    h_deq[(size_t)pair * inter + blockIdx.x * 32 + lane] =
-        __fmul_rn(e4m3_to_float(q), __uint_as_float(bits));
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  const uint32_t bits = mx_scale_bits(amax);
+  const float inv = mx_inverse(bits);
+  const float scale = __uint_as_float(bits);
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    const uint32_t q = e4m3x2(__fmul_rn(v[i], inv), __fmul_rn(v[i + 1], inv));
+    const float2 d = decode2<MACH_FMT_E4M3>(q);
+    v[i] = __fmul_rn(d.x, scale);
+    v[i + 1] = __fmul_rn(d.y, scale);
   }
 }
 
-// ---- w2: one CTA per (token, group of features); warp (f, j) computes y = bf16(dot) of feature
-// f with the token's j-th pair, all pairs of a feature at the same time; then one thread per
-// feature folds them in k order: acc = fma(w_k, y_k, acc). Dynamic shared memory: the
-// dequantised SwiGLU rows of the token's pairs, topk_pad x inter floats.
-__global__ void __launch_bounds__(1024)
-moe_small_w2_kernel(const float* __restrict__ h_deq, const int* __restrict__ pair_expert,
+// ---- w2: one warp per (token, output feature): for every pair of the token, y_k = bf16(dot of
+// the pair's requantised SwiGLU row with the expert's W2 row), four pairs' loads in flight
+// together, then acc = fma(w_k, y_k, acc) in k order.
+template <int kFmt>
+__global__ void __launch_bounds__(128)
+moe_small_w2_kernel(const float* __restrict__ h_val, const int* __restrict__ pair_expert,
                     const float* __restrict__ topk_weights, const uint8_t* __restrict__ w2,
-                    const uint8_t* __restrict__ s2, int topk, int topk_pad, int hidden, int inter,
-                    int fmt, int row_bytes, __nv_bfloat16* __restrict__ out) {
-  extern __shared__ float h_t[];
-  __shared__ float lut[256];
-  __shared__ float ys[32];
+                    const uint8_t* __restrict__ s2, int topk, int hidden, int inter,
+                    int row_bytes, __nv_bfloat16* __restrict__ out) {
   pdl_launch_dependents();
-  load_lut(lut, fmt);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int feats = 32 / topk_pad;             // features per CTA
-  const int f_local = warp / topk_pad;
-  const int j = warp - f_local * topk_pad;
   const int token = blockIdx.y;
-  const int feat = blockIdx.x * feats + f_local;
+  const int feat = blockIdx.x * 4 + warp;
   const int k_tiles = (inter + 127) >> 7;
-  const int units = inter >> 4;
+  const int units = inter >> 4;   // even: inter % 32 == 0
   pdl_wait();
-  const int pair = token * topk + j;
-  const int e = (j < topk && feat < hidden) ? pair_expert[pair] : -1;  // warp-uniform
-  const int64_t row = (int64_t)max(e, 0) * hidden + feat;
-  const uint8_t* r_ptr = w2 + row * row_bytes;
-  WeightUnit w[4];
-  float ws[4];
-  auto fetch = [&](int base) {
+  if (feat >= hidden) return;
+  float acc = 0.0f;
+  for (int j0 = 0; j0 < topk; j0 += 4) {
+    int e[4];
+    float dots[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int unit = base + 32 * i + lane;
-      if (e >= 0 && unit < units) {
-        w[i] = load_unit(r_ptr, unit, fmt);
-        ws[i] = pow2_of_byte(__ldg(s2 + sf_offset((int)row, unit >> 1, k_tiles)));
+    for (int q = 0; q < 4; ++q) e[q] = j0 + q < topk ? pair_expert[token * topk + j0 + q] : -1;
+    for (int base = 0; base < units; base += 32) {
+      const int unit = base + lane;
+      const bool in_range = unit < units;   // pairs of lanes (one 32-block) are in range together
+      WeightUnit w[4];
+      float sc[4];
+      float a[4][16];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (e[q] >= 0 && in_range) {
+          const int64_t row = (int64_t)e[q] * hidden + feat;
+          w[q] = load_unit<kFmt>(w2 + row * row_bytes, unit);
+          sc[q] = pow2_of_byte(__ldg(s2 + sf_offset((int)row, unit >> 1, k_tiles)));
+          load_act16(h_val + (size_t)(token * topk + j0 + q) * inter + unit * 16, a[q]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) a[q][i] = 0.0f;
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (e[q] >= 0) {   // warp-uniform: the shuffle inside sees every lane
+          requant16(a[q]);
+          if (in_range) dots[q] = __fmaf_rn(dot16<kFmt>(w[q], a[q]), sc[q], dots[q]);
+        }
       }
     }
-  };
-  fetch(0);
-  for (int q = 0; q < topk; ++q)
-    if (pair_expert[token * topk + q] >= 0)   // block-uniform
-      stage_transposed(h_t + (size_t)q * inter, h_deq + (size_t)(token * topk + q) * inter, inter);
-  __syncthreads();
-  float y = 0.0f;
-  if (e >= 0) {
-    const float* mine = h_t + (size_t)j * inter;
-    float dot = 0.0f;
-    for (int base = 0; base < units; base += 128) {
-      if (base > 0) fetch(base);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int unit = base + 32 * i + lane;
-        if (unit < units) dot = __fmaf_rn(dot16(w[i], fmt, lut, mine, units, unit), ws[i], dot);
-      }
-    }
+    for (int q = 0; q < 4; ++q) {
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) dot = __fadd_rn(dot, __shfl_xor_sync(0xffffffffu, dot, d));
-    y = bf16_round(dot);
-  }
-  if (lane == 0) ys[warp] = y;
-  __syncthreads();
-  if ((int)threadIdx.x < feats) {
-    const int f = blockIdx.x * feats + threadIdx.x;
-    if (f < hidden) {
-      float acc = 0.0f;
-      for (int q = 0; q < topk; ++q) {
-        const int pr = token * topk + q;
-        if (pair_expert[pr] < 0) continue;
-        acc = __fmaf_rn(topk_weights[pr], ys[threadIdx.x * topk_pad + q], acc);
-      }
-      out[(size_t)token * hidden + f] = __float2bfloat16_rn(acc);
+      for (int d = 16; d > 0; d >>= 1) dots[q] = __fadd_rn(dots[q], __shfl_xor_sync(0xffffffffu, dots[q], d));
+      if (e[q] >= 0) acc = __fmaf_rn(topk_weights[token * topk + j0 + q], bf16_round(dots[q]), acc);
     }
   }
+  if (lane == 0) out[(size_t)token * hidden + feat] = __float2bfloat16_rn(acc);
 }
 
 int launched(cudaError_t e, const char* what) {
@@ -346,24 +338,25 @@ extern "C" int mach_moe_small_batch(const void* hidden_bf16, const void* topk_we
                               (int)topk, (int)hidden, act, pair_expert),
                     "moe_small_front");
   if (rc != MACH_OK) return rc;
-  if (hidden * 4 > 40 * 1024 || 16 * inter * 4 > 40 * 1024)
-    return fail(MACH_ERR_UNSUPPORTED, "moe_small_batch: hidden <= 10240, intermediate <= 640 required");
-  rc = launched(launch_ex(moe_small_w1_kernel, dim3((unsigned)(inter / 32), (unsigned)(m * topk)),
-                          dim3(1024), (size_t)hidden * 4, st, dim3(1, 1, 1), pdl_enabled(),
-                          (const float*)act,
-                          (const int*)pair_expert, (const uint8_t*)w13, (const uint8_t*)s13,
-                          (int)topk, (int)hidden, (int)inter, w_format, row1, h_deq),
-                "moe_small_w1");
-  if (rc != MACH_OK) return rc;
-  int topk_pad = 1;
-  while (topk_pad < topk) topk_pad <<= 1;       // 1, 2, 4, 8, 16: divides the 32 warps of a CTA
-  const int feats = 32 / topk_pad;
-  return launched(launch_ex(moe_small_w2_kernel,
-                            dim3((unsigned)((hidden + feats - 1) / feats), (unsigned)m), dim3(1024),
-                            (size_t)topk_pad * inter * 4, st, dim3(1, 1, 1), pdl_enabled(),
-                            (const float*)h_deq,
-                            (const int*)pair_expert, (const float*)topk_weights_f32,
-                            (const uint8_t*)w2, (const uint8_t*)s2, (int)topk, topk_pad,
-                            (int)hidden, (int)inter, w_format, row2, (__nv_bfloat16*)out_bf16),
-                  "moe_small_w2");
+  const dim3 g1((unsigned)((inter + 3) / 4), (unsigned)(m * topk));
+  const dim3 g2((unsigned)((hidden + 3) / 4), (unsigned)m);
+#define MACH_SMALL_LAUNCH(FMT)                                                                     \
+  do {                                                                                             \
+    rc = launched(launch_ex(moe_small_w1_kernel<FMT>, g1, dim3(128), 0, st, dim3(1, 1, 1),         \
+                            pdl_enabled(), (const float*)act, (const int*)pair_expert,             \
+                            (const uint8_t*)w13, (const uint8_t*)s13, (int)topk, (int)hidden,      \
+                            (int)inter, row1, h_deq),                                              \
+                  "moe_small_w1");                                                                 \
+    if (rc != MACH_OK) return rc;                                                                  \
+    return launched(launch_ex(moe_small_w2_kernel<FMT>, g2, dim3(128), 0, st, dim3(1, 1, 1),       \
+                              pdl_enabled(), (const float*)h_deq, (const int*)pair_expert,         \
+                              (const float*)topk_weights_f32, (const uint8_t*)w2,                  \
+                              (const uint8_t*)s2, (int)topk, (int)hidden, (int)inter, row2,        \
+                              (__nv_bfloat16*)out_bf16),                                           \
+                    "moe_small_w2");                                                               \
+  } while (0)
+  if (w_format == MACH_FMT_E4M3) MACH_SMALL_LAUNCH(MACH_FMT_E4M3);
+  if (w_format == MACH_FMT_E2M3) MACH_SMALL_LAUNCH(MACH_FMT_E2M3);
+  MACH_SMALL_LAUNCH(MACH_FMT_E3M2);
+#undef MACH_SMALL_LAUNCH
 }

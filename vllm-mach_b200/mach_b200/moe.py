@@ -59,9 +59,12 @@ def router_topk(logits: torch.Tensor, top_k: int):
 
 
 # Largest batch that takes the small-batch schedule (three CUDA-core launches; see
-# mach_moe_small_batch). Measured on B200, 256 experts / top-8 / hidden 2048 / intermediate 512:
-# the cross-over with the grouped tensor-core path lies above 8 tokens.
-SMALL_BATCH_MAX_TOKENS = 8
+# mach_moe_small_batch; the entry point itself accepts up to 8 tokens). Measured on B200,
+# 256 experts / top-8 / hidden 2048 / intermediate 512, CUDA-graph replay: one token 21.6 us
+# against 28.9 us for route + gather + two grouped GEMMs + combine; the CUDA-core products cost
+# about 17 us per further token (instruction-bound), the grouped path about 1-3 us (4 tokens:
+# 67.8 against 32.7 us), so only single-token decode takes it.
+SMALL_BATCH_MAX_TOKENS = 1
 
 
 def chunk_rows_for(tokens: int, top_k: int, experts: int) -> int:
