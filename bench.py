@@ -42,7 +42,7 @@ NUM_WEIGHT_SETS = 4       # 4 x 77 MB > 126 MB L2: weights always come from HBM
 CPU_SAMPLE_TOKENS = HEADLINE_M   # the CPU arm runs the GPU arm's configuration
 SOAK_SECONDS = 1.0
 KERNEL_TIMING_LAUNCHES = 200     # launches of the dominant kernel timed one by one
-OWNER_MIN_BYTES = 256 << 10      # tensor-parallel payloads above this take the owner form
+OWNER_MIN_BYTES = 1 << 20        # tensor-parallel payloads above this take the owner form
 TRAFFIC_FILE = ROOT / "profiles" / "ncu_traffic.json"
 
 
