@@ -57,6 +57,9 @@ struct ArWorkspace {
   size_t owner_partial_off;     // owner form: BF16 partial sums [tokens_cap, hidden]
   size_t owner_stage_off;       // owner form: codes [tokens_cap, hidden] then scales [tokens_cap, hidden/32]
   long long wait_cycles;
+#ifdef MACH_EXPERIMENTS
+  unsigned long long* trace;
+#endif
   uint8_t* peers[kMaxWorld];    // peers[rank] is this rank's own buffer
   // hand-off from mach_mx_gemm_reduce_scatter to the reduce that follows it
   int scatter_pending, scattered_one_shot;
@@ -82,14 +85,33 @@ struct ArParams {
   int coarse;              // two-shot: one flag per (rank, phase) instead of one per CTA
   int owner;               // owner form
   size_t parity_bytes, owner_partial_off, owner_stage_off;
+#ifdef MACH_EXPERIMENTS
+  unsigned long long* trace;  // phase time stamps of CTA 0: [epoch % 64][8] (globaltimer, ns)
+#endif
 };
+
+#ifdef MACH_EXPERIMENTS
+__device__ __forceinline__ void trace_stamp(const ArParams& p, uint32_t epoch, int slot) {
+  if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.trace[(epoch & 63u) * 8 + slot] = t;
+  }
+}
+#define MACH_TRACE(p, epoch, slot) trace_stamp(p, epoch, slot)
+#else
+#define MACH_TRACE(p, epoch, slot)
+#endif
 
 struct ArParamsMulti {
   ArParams r[kMaxWorld];
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// A flag store that follows ONE system-scope fence (`__threadfence_system()`): fence + relaxed
+// stores are a release pattern, and every st.release.sys would pay the fence again (measured
+// on two B200s: about 2 us per system-scope fence, i.e. 2 us per destination rank).
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -191,7 +213,7 @@ __device__ __forceinline__ void publish_phase(const ArParams& p, uint32_t* count
       __threadfence_system();
       for (int d = 1; d < p.world; ++d) {
         uint8_t* peer = p.peers[(p.rank + d) % p.world];
-        st_release_sys(gather ? gather_flag(peer, p.rank, 0) : scatter_flag(peer, p.rank, 0), target);
+        st_relaxed_sys(gather ? gather_flag(peer, p.rank, 0) : scatter_flag(peer, p.rank, 0), target);
       }
     }
   }
@@ -328,10 +350,12 @@ __device__ __forceinline__ void owner_body(const ArParams& p, uint8_t* mine, uin
     if (cta == 0 && threadIdx.x == 0) {
       __threadfence_system();
       for (int d = 1; d < p.world; ++d)
-        st_release_sys(scatter_flag(p.peers[(p.rank + d) % p.world], p.rank, 0), target);
+        st_relaxed_sys(scatter_flag(p.peers[(p.rank + d) % p.world], p.rank, 0), target);
     }
   }
+  MACH_TRACE(p, target - 1, 1);
   if (!poison) poison = wait_peers(p, mine, false, 0, target, kWaitScatter);
+  MACH_TRACE(p, target - 1, 2);
 
   // ---- (1) my rows: pull from every rank, sum in rank order, residual + norm + quant.
   // With kPrefetch the loads of the CTA's NEXT row are issued before the current row is
@@ -394,12 +418,15 @@ __device__ __forceinline__ void owner_body(const ArParams& p, uint8_t* mine, uin
       for (int src = 0; src < kMaxWorld; ++src) cur[src] = nxt[src];
     }
   }
+  MACH_TRACE(p, target - 1, 3);
   if (!failed_before) {
     // also after a late scatter flag: the peers still expect this rank's gather flag
     publish_phase(p, ctrl + kCtrlTicketB, true, target, ctas);
+    MACH_TRACE(p, target - 1, 4);
     const bool late = wait_peers(p, mine, true, 0, target, kWaitGather);
     poison = poison || late;
   }
+  MACH_TRACE(p, target - 1, 5);
 
   // ---- (2) the other owners' codes and scales. One flat index space over (owner, vector):
   // a thread first issues up to eight peer loads (different owners, all in flight together),
@@ -512,7 +539,7 @@ __device__ __forceinline__ void push_body(const ArParams& p, uint8_t* mine, uint
       __threadfence_system();
       for (int d = 1; d < p.world; ++d) {
         const int dst = (p.rank + d) % p.world;
-        st_release_sys(scatter_flag(p.peers[dst], p.rank, cta), target);
+        st_relaxed_sys(scatter_flag(p.peers[dst], p.rank, cta), target);
       }
     }
     if (!poison) poison = wait_peers(p, mine, false, cta, target, kWaitScatter);
@@ -564,7 +591,7 @@ __device__ __forceinline__ void push_body(const ArParams& p, uint8_t* mine, uint
     if (threadIdx.x == 0) {
       __threadfence_system();
       for (int d = 1; d < p.world; ++d)
-        st_release_sys(scatter_flag(p.peers[(p.rank + d) % p.world], p.rank, cta), target);
+        st_relaxed_sys(scatter_flag(p.peers[(p.rank + d) % p.world], p.rank, cta), target);
     }
   }
   if (!poison) poison = wait_peers(p, mine, false, p.coarse ? 0 : cta, target, kWaitScatter);
@@ -603,7 +630,7 @@ __device__ __forceinline__ void push_body(const ArParams& p, uint8_t* mine, uint
       if (threadIdx.x == 0) {
         __threadfence_system();
         for (int d = 1; d < p.world; ++d)
-          st_release_sys(gather_flag(p.peers[(p.rank + d) % p.world], p.rank, cta), target);
+          st_relaxed_sys(gather_flag(p.peers[(p.rank + d) % p.world], p.rank, cta), target);
       }
     }
     const bool late = wait_peers(p, mine, true, p.coarse ? 0 : cta, target, kWaitGather);
@@ -655,10 +682,12 @@ __device__ __forceinline__ void ar_body(const ArParams& p) {
   __syncthreads();
   const uint32_t epoch = s_epoch;
   const bool failed_before = s_failed != 0;
+  MACH_TRACE(p, epoch, 0);
   if (failed_before && blockIdx.x == 0 && threadIdx.x == 0) report_timeout(p.status, kWorkspaceFailed);
   if (p.owner) owner_body<kPrefetch>(p, mine, ctrl, epoch + 1, failed_before, warp_sums);
   else push_body(p, mine, ctrl, epoch, failed_before, warp_sums);
 
+  MACH_TRACE(p, epoch, 6);
   // ---- the last CTA to finish advances the epoch for the next launch
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -667,7 +696,7 @@ __device__ __forceinline__ void ar_body(const ArParams& p) {
     if (done == gridDim.x - 1) {
       ctrl[kCtrlDone] = 0;
       __threadfence();
-      st_release_sys(ctrl + kCtrlEpoch, epoch + 1);
+      ctrl[kCtrlEpoch] = epoch + 1;   // read by this GPU's next launch only
     }
   }
 }
@@ -749,6 +778,9 @@ int fill_params(ArWorkspace* ws, const void* partial, const void* residual, cons
   p.status = device_status_ptr();
   if (!p.status) return fail(MACH_ERR_CUDA, "allreduce_rmsnorm: cannot resolve the status word");
   p.wait_cycles = ws->wait_cycles;
+#ifdef MACH_EXPERIMENTS
+  p.trace = ws->trace;
+#endif
   p.eps = eps;
   p.weight_bias = weight_bias;
   p.rank = ws->rank;
@@ -990,6 +1022,16 @@ extern "C" int mach_ar_set_wait_limit_us(void* workspace, int64_t microseconds) 
   ws->wait_cycles = (long long)microseconds * (long long)khz / 1000;
   return MACH_OK;
 }
+
+#ifdef MACH_EXPERIMENTS
+// Experiment builds only: device buffer of 64 x 8 time stamps (ns) written by CTA 0.
+extern "C" __attribute__((visibility("default"))) int mach_ar_set_trace(void* workspace, void* dev) {
+  ArWorkspace* ws = reinterpret_cast<ArWorkspace*>(workspace);
+  if (!ws) return fail(MACH_ERR_INVALID, "ar_set_trace: null workspace");
+  ws->trace = reinterpret_cast<unsigned long long*>(dev);
+  return MACH_OK;
+}
+#endif
 
 extern "C" int mach_ar_reset(void* workspace, void* stream) {
   ArWorkspace* ws = reinterpret_cast<ArWorkspace*>(workspace);
