@@ -400,7 +400,9 @@ MACH_API int mach_moe_work_from_offsets(const void* expert_offsets_i64,
  * "split" (cluster size along K of the feature-major GEMM: 1..8), "split_fill_pct" (grow the
  * cluster until CTAs reach this percentage of the SM count), "stages" (pipeline
  * depth), "bn" (token-major N tile: 128, 256), "swap_max_m" (largest batch handled
- * feature-major, <= 64), "smem_cap_kb" (cap on dynamic shared memory per CTA), "tm_min_m"
+ * feature-major at all), "wide_max_m" / "narrow_max_m" (largest batch a wide / a narrow weight
+ * matrix runs feature-major; heuristic 32-64 / 256), "mid" (0: batches up to 128 tokens skip
+ * the one-token-tile kernel), "smem_cap_kb" (cap on dynamic shared memory per CTA), "tm_min_m"
  * (smallest batch for the persistent 256-token kernels), "tm_bn" (their tile width), "pair"
  * (0: single-CTA persistent kernel instead of the cta_group::2 kernel), "panel_m"
  * (raster panel height). A library built with -DMACH_EXPERIMENTS (kernel sweeps only) also

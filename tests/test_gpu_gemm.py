@@ -162,3 +162,63 @@ def test_large_batch_kernels_agree_bit_for_bit(nat, pair, m, n, k):
     finally:
         nat.tune("pair", -1)
     assert bytes_equal(out, other)
+
+
+# One token tile (49..128 tokens) and a weight matrix with at least one 64-row group per SM:
+# balanced variable-width tiles. 9728 rows: 1-2 groups per CTA; 19456: 2-3; 66304: 7 (two MMAs,
+# 256 + 192 columns); 85248: two rounds of CTAs; 9744: a partial last group.
+@pytest.mark.parametrize("m,n,k", [(65, 9728, 384), (128, 19456, 256), (100, 66304, 128),
+                                   (80, 85248, 128), (128, 9744, 160), (65, 19456, 2560)])
+def test_one_token_tile_kernel_matches_dequant_matmul(nat, m, n, k):
+    out, ref = run_gemm(nat, m, n, k, seed=3000 + m)
+    assert torch.isfinite(out.float()).all()
+    assert torch.allclose(out.float(), ref.float(), rtol=0.01, atol=0.02), \
+        f"max abs err {float((out.float() - ref.float()).abs().max())}"
+    assert rel_fro(out, ref) <= 1e-2
+    # the 256-token pair kernel accumulates over K in the same order: identical bytes
+    nat.tune("mid", 0)
+    try:
+        other, _ = run_gemm(nat, m, n, k, seed=3000 + m)
+    finally:
+        nat.tune("mid", 1)
+    assert bytes_equal(out, other), mismatch_report(out, other)
+
+
+@pytest.mark.parametrize("m,inter,k", [(49, 4864, 256), (128, 9728, 2560), (96, 33152, 128)])
+def test_one_token_tile_swiglu_bit_exact(nat, m, inter, k):
+    x = randn_bf16(m, k, 5000 + m)
+    w_codes, w_scales, _ = mxfp8_weight(2 * inter, k, 5001 + m, sigma=0.05)
+    a_dev, sa_dev = nat.quantize_mxfp8(x.cuda())
+    wi, si = interleaved_weight(nat, w_codes, w_scales, k)
+    gate_up = nat.mx_gemm(a_dev, sa_dev, wi, si, layout=nat.LAYOUT_GATE_UP_32)
+    rows = nat.mx_gemm(a_dev, sa_dev, w_codes.cuda(), nat.pack_scales(w_scales.cuda(), k))
+    if m > 64:   # both token-major: the same K order
+        assert bytes_equal(gate_up, rows), mismatch_report(gate_up, rows)
+    else:        # the row layout runs feature-major with a cluster split of K up to 64 tokens
+        assert torch.allclose(gate_up.float(), rows.float(), rtol=0.01, atol=0.02)
+    codes, scales = nat.mx_gemm_swiglu(a_dev, sa_dev, wi, si, layout=nat.LAYOUT_GATE_UP_32)
+    torch.cuda.synchronize()
+    assert nat.device_status() == 0
+    ref_codes, ref_scales = ora.swiglu_quantize(gate_up.cpu())
+    assert torch.equal(ora.unswizzle_scales(scales.cpu(), m, inter), ref_scales)
+    assert bytes_equal(codes, ref_codes), mismatch_report(codes, ref_codes)
+    nat.tune("mid", 0)
+    try:
+        codes2, scales2 = nat.mx_gemm_swiglu(a_dev, sa_dev, wi, si, layout=nat.LAYOUT_GATE_UP_32)
+    finally:
+        nat.tune("mid", 1)
+    assert bytes_equal(codes, codes2)
+    assert torch.equal(ora.unswizzle_scales(scales2.cpu(), m, inter), ref_scales)
+
+
+# Narrow plain GEMMs stay feature-major (cluster split-K) up to 256 tokens; from 208 tokens the
+# receive slots of the exchange reuse the operand ring.
+@pytest.mark.parametrize("m,n,k", [(200, 2560, 9728), (256, 2560, 9728), (224, 512, 2048),
+                                   (256, 384, 416)])
+def test_feature_major_wide_batch(nat, m, n, k):
+    out, ref = run_gemm(nat, m, n, k, seed=6000 + m)
+    out2, _ = run_gemm(nat, m, n, k, seed=6000 + m)
+    assert bytes_equal(out, out2)
+    assert torch.allclose(out.float(), ref.float(), rtol=0.01, atol=0.02), \
+        f"max abs err {float((out.float() - ref.float()).abs().max())}"
+    assert rel_fro(out, ref) <= 1e-2

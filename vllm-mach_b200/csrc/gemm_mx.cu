@@ -61,6 +61,8 @@ struct MxGemmParams {
   int debug;             // experiment bits: 1 skip scale copies, 2 skip MMAs, 8 alternate SF columns
   int interleaved;       // weight rows are gate/up interleaved by 32 (plain epilogue remaps)
   int tx_discount;       // bytes per stage TMA does not count: packed 6-bit rows report 96 of 128
+  int recv_off;          // feature-major: byte offset of the receive slots (0: they reuse the ring)
+  int bars_off;          // byte offset of the barriers
 };
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -81,7 +83,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int bn = p.bn;
-  const int num_q_sf = kSwap ? 1 : bn / 128;
+  const int num_q_sf = kSwap ? (bn + 127) / 128 : bn / 128;  // scale atoms cover 128 rows
   const int q_bytes = bn * kTileK;
   const int sf_off = kNumP * kTileBytes + q_bytes;
   const int tx_bytes = sf_off + (kNumP + num_q_sf) * kSfAtom - p.tx_discount;
@@ -92,9 +94,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   // fewer, possibly none)
   const int cols_owned = (bn + split - 1) / split;
 
-  float* recv = reinterpret_cast<float*>(smem + (size_t)stages * stage_bytes);
-  const int recv_bytes = kSwap ? kNumP * kTileRows * split * cols_owned * 4 : 0;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(recv) + recv_bytes);
+  // Receive slots of the K-split exchange. Wide batches have no room for them beside the ring:
+  // they then reuse it (recv_off == 0), and one more cluster barrier keeps every CTA's partial
+  // sums out of a ring that its owner's MMAs still read.
+  float* recv = reinterpret_cast<float*>(smem + p.recv_off);
+  const bool recv_in_ring = kSwap && p.recv_off == 0 && split > 1;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.bars_off);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 1);
   const uint32_t full0 = smem_u32(bars);
   const uint32_t empty0 = smem_u32(bars + kMaxStages);
@@ -228,6 +233,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       __syncwarp();
       if (++s == stages) { s = 0; ph ^= 1u; }
     }
+    if (recv_in_ring) cluster_sync_all();
   } else if (warp == 1) {
     // =============================== MMA issuer (warp-uniform loop, one elected lane issues)
     // The issuing thread bounds the kernel: descriptors are 32-bit low words that only need an
@@ -290,12 +296,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     }
     if (elect_one()) tc_commit(accum_bar);
     __syncwarp();
+    if (recv_in_ring) cluster_sync_all();
   } else {
     // =============================== epilogue warps
     const int quad = warp & 3;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
     const bool ready = mbar_wait(accum_bar, 0, p.status, kWaitAccum);
     tc_fence_after();
+    // every CTA of the cluster has finished reading its ring (its accumulator is complete)
+    if (recv_in_ring) cluster_sync_all();
     if (!kSwap) {
       const int row = m0 + quad * 32 + lane;
       if (!kSwiglu) {
@@ -520,6 +529,8 @@ int make_bf16_store_map(CUtensorMap* map, const void* base, int64_t rows, int64_
 }
 
 int run_mx_gemm_pair(const TmGemmArgs& args, cudaStream_t stream);
+int run_mx_gemm_mid(const TmGemmArgs& args, cudaStream_t stream);
+bool mx_gemm_mid_fits(int64_t m, int64_t w_rows);
 int last_pair_count();
 
 namespace {
@@ -540,6 +551,9 @@ struct Tuning {
   int tm_bn = 0;           // its tile width in weight rows (0 = 192)
   int pair = -1;           // large batches: 1 or -1 (default) = cta_group::2 kernel,
                            // 0 = single-CTA persistent kernel
+  int mid = 1;             // 0: batches of 49..128 tokens skip the one-token-tile kernel
+  int narrow_max_m = 256;  // largest batch a narrow plain GEMM runs feature-major
+  int wide_max_m = 0;      // largest batch a wide GEMM runs feature-major (0 = heuristic)
 };
 Tuning g_tune;
 
@@ -566,16 +580,8 @@ template <bool kSwap, bool kSwiglu, bool kIl>
 int launch(const CUtensorMap& tm_p, const CUtensorMap& tm_q, MxGemmParams& prm, dim3 grid,
            int smem_bytes, cudaStream_t stream) {
   auto kernel = mx_gemm_kernel<kSwap, kSwiglu, kIl>;
-  static int configured_smem_dev[kMaxDeviceSlots] = {};  // the attribute is per device
-  int& configured_smem = configured_smem_dev[device_slot()];
-  if (smem_bytes > configured_smem) {
-    const cudaError_t e =
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e != cudaSuccess)
-      return fail(MACH_ERR_CUDA, "mx_gemm: cannot opt in to %d B of shared memory: %s", smem_bytes,
-                  cudaGetErrorString(e));
-    configured_smem = smem_bytes;
-  }
+  if (!ensure_smem_optin(reinterpret_cast<const void*>(kernel)))
+    return fail(MACH_ERR_CUDA, "mx_gemm: cannot opt in to %d B of shared memory", max_smem_optin());
   const cudaError_t e =
       launch_ex(kernel, grid, dim3(kThreads), (size_t)smem_bytes, stream,
                 dim3(1, (kSwap && prm.split > 1) ? (unsigned)prm.split : 1u, 1), pdl_enabled(), tm_p,
@@ -634,21 +640,32 @@ int run_mx_gemm(const void* a_codes, const void* a_sf, const void* w, const void
   if (interleaved && (swiglu ? n % 32 : n % 64))
     return fail(MACH_ERR_UNSUPPORTED, "%s: interleaved gate_up needs I %% 32 == 0", what);
   const int64_t w_rows = swiglu ? 2 * n : n;
-  // Feature-major (cluster split-K) up to 48 tokens (interleaved layouts; 64 for plain row
-  // layouts, whose token-major SwiGLU needs the 128-token kernel), and up to 192 for plain GEMMs
-  // whose N gives the token-major kernels too few tiles to fill the machine. Measured on B200:
-  // 19456 x 2560 gate_up at M = 64: 16.6 us token-major against 22.7; 2560 x 9728 down at
-  // M = 96..192: 16-23 us feature-major against 29.
+  // Which orientation. Feature-major (weights on the 128-row side, cluster split-K) wins while
+  // the batch is a small MMA-N; measured on B200 (graph replay, us):
+  //   19456 x 2560 interleaved gate_up + SwiGLU   M = 32: 17.2 feature-major / 20.3 one token tile
+  //                                               M = 48: 20.3 / 19.1      M = 64: 22.7 / 17.5
+  //   19456 x 2560 plain rows, BF16 out           M = 32: 15.0 / 15.6      M = 48: 17.3 / 15.3
+  //                                               M = 64: 22.9 / 13.9
+  //   2560 x 9728 (narrow: too few tiles for the token-major kernels)
+  //                                               M = 192: 20.3 / 29 (pair)   M = 256: 24.9 / 28.1
   const bool narrow = !swiglu && (n + 127) / 128 * 4 <= sm_count();
-  const int64_t wide_max = interleaved ? 48 : 64;
-  const bool swap = m <= g_tune.swap_max_m && (m <= wide_max || (narrow && m <= 192));
+  const bool mid_layout = interleaved || !swiglu;   // layouts the one-token-tile kernel takes
+  const bool mid_shape = g_tune.mid != 0 && !scatter && mid_layout && mx_gemm_mid_fits(128, w_rows);
+  const int64_t wide_max = g_tune.wide_max_m > 0 ? g_tune.wide_max_m
+                           : (swiglu && interleaved) ? 48
+                           : mid_shape ? 32 : 64;
+  const bool swap =
+      m <= g_tune.swap_max_m && (m <= wide_max || (narrow && m <= g_tune.narrow_max_m));
   const bool token_major_pair =
       ((!swap && m >= g_tune.tm_min_m && (!swiglu || interleaved)) || (interleaved && !swap));
   if (scatter && (!token_major_pair || g_tune.pair == 0))
     return fail(MACH_ERR_UNSUPPORTED,
                 "%s: this shape does not take the CTA-pair kernel; run the plain GEMM and the "
                 "all-reduce separately", what);
-  if (token_major_pair) {
+  // One token tile and a weight matrix wide enough to give every SM its own rows: balanced
+  // variable-width tiles in one round (measured on B200 against the 256-token pair tiles).
+  const bool one_tile = !swap && mid_shape && mx_gemm_mid_fits(m, w_rows);
+  if (token_major_pair || one_tile) {
     TmGemmArgs args = {};
     args.scatter = scatter;
     args.a_codes = a_codes; args.a_sf = a_sf; args.w = w; args.w_sf = w_sf;
@@ -660,6 +677,8 @@ int run_mx_gemm(const void* a_codes, const void* a_sf, const void* w, const void
     if (scatter && g_tune.tm_bn == 0) args.bn = std::min(args.bn, 192);
     args.stages = g_tune.force_stages; args.panel_m = g_tune.panel_m;
     args.debug = g_tune.debug;
+    args.smem_cap_kb = g_tune.smem_cap_kb;
+    if (one_tile) return run_mx_gemm_mid(args, stream);
     const bool pair = g_tune.pair != 0;
     return pair ? run_mx_gemm_pair(args, stream) : run_mx_gemm_tm(args, stream);
   }
@@ -722,7 +741,7 @@ int run_mx_gemm(const void* a_codes, const void* a_sf, const void* w, const void
     prm.stream_weights = (m <= 128) ? 1 : 0;
   }
   prm.bn = bn;
-  const int num_q_sf = swap ? 1 : bn / 128;
+  const int num_q_sf = swap ? (bn + 127) / 128 : bn / 128;
   const int acc_cols = num_p * bn;
   prm.debug = g_tune.debug;
   prm.tmem_cols = next_pow2_cols(acc_cols + 2 * (4 * num_p + 4 * num_q_sf));
@@ -740,44 +759,64 @@ int run_mx_gemm(const void* a_codes, const void* a_sf, const void* w, const void
   // receive slots: [tile][source rank][owned column][128 rows]; sized for the largest cluster
   // the heuristic below may still shrink to, so the plan does not depend on that choice
   const int recv_bytes = swap ? num_p * kTileRows * (bn + 7) * 4 : 0;
-  const int fixed = recv_bytes + (2 * kMaxStages + 1) * 8 + 16 + 1024;
+  const int tail = (2 * kMaxStages + 1) * 8 + 16 + 1024;
+  // Wide batches: two stages and the receive slots do not fit side by side; the slots then
+  // reuse the ring once every CTA of the cluster has finished its MMAs.
+  const bool reuse_ring = swap && 2 * stage_bytes + recv_bytes + tail > max_smem_optin();
+  auto plan_bytes = [&](int st) {
+    return (reuse_ring ? std::max(st * stage_bytes, recv_bytes) : st * stage_bytes + recv_bytes) + tail;
+  };
   int budget = max_smem_optin();
   // Feature-major CTAs stay small (three per SM) so that every CTA of the grid is resident at
   // once and a dependent kernel finds room to prefetch its weights.
-  if (swap) budget = std::min(budget, std::max(70 * 1024, fixed + 3 * stage_bytes));
+  // Grids of at most two CTAs per SM may take half an SM each: measured on B200, 2560 x 9728 at
+  // M = 16 (160 CTAs): 7.1 us with five stages in 110 KB against 7.6 us with three in 70 KB.
+  const int small_cta = tiles * prm.split <= 2 * (int64_t)sm_count() ? 110 * 1024 : 70 * 1024;
+  if (swap && !reuse_ring) budget = std::min(budget, std::max(small_cta, plan_bytes(3)));
   if (g_tune.smem_cap_kb > 0) budget = std::min(max_smem_optin(), g_tune.smem_cap_kb * 1024);
-  int stages = (budget - fixed) / stage_bytes;
-  stages = std::min(stages, kMaxStages);
-  if (g_tune.force_stages > 0) stages = std::min(stages, g_tune.force_stages);
-  if (stages < 1) return fail(MACH_ERR_UNSUPPORTED, "%s: tile does not fit in shared memory", what);
+  int stages = std::min(kMaxStages, g_tune.force_stages > 0 ? g_tune.force_stages : kMaxStages);
+  while (stages > 1 && plan_bytes(stages) > budget) --stages;
+  if (plan_bytes(stages) > max_smem_optin())
+    return fail(MACH_ERR_UNSUPPORTED, "%s: tile does not fit in shared memory", what);
   stages = std::max(1, std::min(stages, swap ? (prm.k_tiles + prm.split - 1) / prm.split : prm.k_tiles));
-  prm.stages = stages;
-  int smem_bytes = stages * stage_bytes + fixed;
-  if (swap && g_tune.force_split == 0) {
-    // Every CTA of the grid should be resident at once (a second, nearly empty wave doubles
-    // the time of a 10 us kernel). First give up ring depth (two stages per CTA still leave
-    // several stages in flight per SM), only then shrink the cluster.
-    auto resident = [&](int st) {
-      const int bytes = st * stage_bytes + fixed;
-      return (int64_t)std::max(1, std::min((228 * 1024) / (bytes + 1024), 512 / prm.tmem_cols)) *
-             sm_count();
-    };
-    if (tiles * prm.split > resident(stages) && stages > 2 && g_tune.force_stages == 0 &&
-        tiles * prm.split <= resident(2)) {
-      stages = 2;
-      prm.stages = stages;
-      smem_bytes = stages * stage_bytes + fixed;
-    }
-    while (prm.split > 1 && tiles * prm.split > resident(stages))
-      prm.split = prm.split > 2 && (prm.split & (prm.split - 1)) ? prm.split - 1 : prm.split >> 1;
-    grid = dim3((unsigned)tiles, (unsigned)prm.split, 1);
-  }
   // Co-resident CTAs must never over-subscribe TMEM: a CTA blocked in tcgen05.alloc while a
   // cluster peer waits for it could deadlock. Pad shared memory until residency is safe.
-  const int max_resident = 512 / prm.tmem_cols;
-  const int sm_smem = 228 * 1024;
-  if ((sm_smem / (smem_bytes + 1024)) > max_resident)
-    smem_bytes = sm_smem / (max_resident + 1) + 1;
+  auto padded_bytes = [&](int st) {
+    const int max_resident = 512 / prm.tmem_cols;
+    const int sm_smem = 228 * 1024;
+    int bytes = plan_bytes(st);
+    if ((sm_smem / (bytes + 1024)) > max_resident) bytes = sm_smem / (max_resident + 1) + 1;
+    return bytes;
+  };
+  const void* kfn =
+      !swap ? (swiglu ? reinterpret_cast<const void*>(mx_gemm_kernel<false, true, false>)
+                      : reinterpret_cast<const void*>(mx_gemm_kernel<false, false, false>))
+            : (!swiglu ? reinterpret_cast<const void*>(mx_gemm_kernel<true, false, false>)
+                       : (interleaved ? reinterpret_cast<const void*>(mx_gemm_kernel<true, true, true>)
+                                      : reinterpret_cast<const void*>(mx_gemm_kernel<true, true, false>)));
+  if (swap && g_tune.force_split == 0) {
+    // Every CTA of the grid should be resident at once (a second, nearly empty wave doubles
+    // the time of a 10 us kernel). With one CTA per SM a cluster must also find its SMs inside
+    // one GPC, so there the device is asked how many clusters of the size it keeps resident
+    // (fewer than SMs / size). First give up ring depth (two stages per CTA still leave
+    // several stages in flight per SM), only then shrink the cluster.
+    auto fits = [&](int st, int sp) {
+      const int bytes = padded_bytes(st);
+      const int per_sm = std::max(1, std::min((228 * 1024) / (bytes + 1024), 512 / prm.tmem_cols));
+      if (tiles * sp > (int64_t)per_sm * sm_count()) return false;
+      if (per_sm == 1 && sp > 1) return tiles <= active_clusters(kfn, kThreads, bytes, sp);
+      return true;
+    };
+    if (!fits(stages, prm.split) && stages > 2 && g_tune.force_stages == 0 && fits(2, prm.split))
+      stages = 2;
+    while (prm.split > 1 && !fits(stages, prm.split)) --prm.split;
+    stages = std::max(1, std::min(stages, (prm.k_tiles + prm.split - 1) / prm.split));
+    grid = dim3((unsigned)tiles, (unsigned)prm.split, 1);
+  }
+  prm.stages = stages;
+  const int smem_bytes = padded_bytes(stages);
+  prm.recv_off = reuse_ring ? 0 : stages * stage_bytes;
+  prm.bars_off = plan_bytes(stages) - tail;
   if (smem_bytes > max_smem_optin())
     return fail(MACH_ERR_UNSUPPORTED, "%s: shared memory plan exceeds the device limit", what);
 
@@ -861,6 +900,9 @@ extern "C" int mach_tune_set(const char* name, int value) {
   else if (!strcmp(name, "tm_min_m")) g_tune.tm_min_m = value > 0 ? value : 65;
   else if (!strcmp(name, "tm_bn")) g_tune.tm_bn = value;
   else if (!strcmp(name, "pair")) g_tune.pair = value;  // pass -1 for the default
+  else if (!strcmp(name, "mid")) g_tune.mid = value;
+  else if (!strcmp(name, "narrow_max_m")) g_tune.narrow_max_m = value;
+  else if (!strcmp(name, "wide_max_m")) g_tune.wide_max_m = value;
   else if (!strcmp(name, "pdl")) mach::set_pdl_enabled(value != 0);
   else return mach::fail(MACH_ERR_INVALID, "tune_set: unknown knob '%s'", name);
   return MACH_OK;

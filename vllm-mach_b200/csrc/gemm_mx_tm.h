@@ -34,6 +34,7 @@ struct TmGemmArgs {
   int stages;            // 0 = fill shared memory
   int panel_m;           // 0 = default raster
   int debug;             // experiment bits (pair kernel)
+  int smem_cap_kb;       // one-token-tile kernel: cap on dynamic shared memory (0 = heuristic)
   const ScatterTarget* scatter;  // non-null: BF16 rows go to the owners' all-reduce buffers
 };
 

@@ -1,6 +1,8 @@
 #include "host_util.h"
 #include <cstdarg>
 #include <cstring>
+#include <mutex>
+#include <vector>
 #include "ptx.cuh"
 
 namespace mach {
@@ -52,6 +54,60 @@ int device_slot() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return 0;
   return dev < kMaxDeviceSlots ? dev : kMaxDeviceSlots - 1;
+}
+
+namespace {
+std::mutex g_occ_mu;
+struct OptinEntry { const void* kernel; int dev; };
+struct OccEntry { const void* kernel; int dev, threads, smem, cluster; int64_t clusters; };
+std::vector<OptinEntry> g_optin;
+std::vector<OccEntry> g_occ;
+}  // namespace
+
+bool ensure_smem_optin(const void* kernel) {
+  const int dev = device_slot();
+  std::lock_guard<std::mutex> lock(g_occ_mu);
+  for (const OptinEntry& e : g_optin)
+    if (e.kernel == kernel && e.dev == dev) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin()) !=
+      cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  g_optin.push_back({kernel, dev});
+  return true;
+}
+
+int64_t active_clusters(const void* kernel, int threads, int smem_bytes, int cluster_y) {
+  const int dev = device_slot();
+  {
+    std::lock_guard<std::mutex> lock(g_occ_mu);
+    for (const OccEntry& e : g_occ)
+      if (e.kernel == kernel && e.dev == dev && e.threads == threads && e.smem == smem_bytes &&
+          e.cluster == cluster_y)
+        return e.clusters;
+  }
+  // Fallback when the query is refused: whole SMs, one CTA each.
+  int64_t clusters = sm_count() / std::max(1, cluster_y);
+  if (ensure_smem_optin(kernel)) {
+    cudaLaunchConfig_t q = {};
+    q.gridDim = dim3((unsigned)sm_count(), (unsigned)cluster_y, 1);
+    q.blockDim = dim3((unsigned)threads);
+    q.dynamicSmemBytes = (size_t)smem_bytes;
+    cudaLaunchAttribute qa[1];
+    qa[0].id = cudaLaunchAttributeClusterDimension;
+    qa[0].val.clusterDim.x = 1;
+    qa[0].val.clusterDim.y = (unsigned)cluster_y;
+    qa[0].val.clusterDim.z = 1;
+    q.attrs = qa;
+    q.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) == cudaSuccess && n > 0) clusters = n;
+    else (void)cudaGetLastError();
+  }
+  std::lock_guard<std::mutex> lock(g_occ_mu);
+  g_occ.push_back({kernel, dev, threads, smem_bytes, cluster_y, clusters});
+  return clusters;
 }
 
 bool pdl_enabled() { return g_pdl; }

@@ -21,6 +21,14 @@ int sm_count();
 // Opt-in shared memory limit per block of the current device.
 int max_smem_optin();
 
+// Raises the kernel's dynamic shared memory limit to the device's opt-in maximum (once per
+// kernel and device). False if the attribute cannot be set.
+bool ensure_smem_optin(const void* kernel);
+// How many clusters of `cluster_y` CTAs (block of `threads`, `smem_bytes` of dynamic shared
+// memory each) the current device keeps resident at once, as cudaOccupancyMaxActiveClusters
+// reports it; cached. A cluster lives inside one GPC, so this can be fewer than SMs / cluster_y.
+int64_t active_clusters(const void* kernel, int threads, int smem_bytes, int cluster_y);
+
 // Device address of the status word of the current device (NULL if it cannot be resolved).
 int* device_status_ptr();
 

@@ -16,7 +16,7 @@ CSRC = PKG.parent / "csrc"
 OBJ = PKG.parent / "build"
 LIB = PKG / "libmach_b200.so"
 HEADER = PKG.parent.parent / "include" / "mach_b200.h"
-SOURCES = ["host_util.cu", "quant_kernels.cu", "gemm_mx.cu", "gemm_mx_tm.cu", "gemm_mx_2cta.cu",
+SOURCES = ["host_util.cu", "quant_kernels.cu", "gemm_mx.cu", "gemm_mx_tm.cu", "gemm_mx_2cta.cu", "gemm_mx_mid.cu",
            "gemm_blockfp8.cu", "gemm_blockfp8_tm.cu", "ar_norm.cu", "moe.cu", "moe_small.cu", "gemm_mx_grouped.cu"]
 FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
