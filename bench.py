@@ -41,6 +41,7 @@ EPS = 1e-6
 NUM_WEIGHT_SETS = 4       # 4 x 77 MB > 126 MB L2: weights always come from HBM
 CPU_SAMPLE_TOKENS = HEADLINE_M   # the CPU arm runs the GPU arm's configuration
 SOAK_SECONDS = 1.0
+STEP_VARIANTS = 4         # step i uses input i % 4 and weight set i % NUM_WEIGHT_SETS
 KERNEL_TIMING_LAUNCHES = 200     # launches of the dominant kernel timed one by one
 OWNER_MIN_BYTES = 1 << 20        # tensor-parallel payloads above this take the owner form
 TRAFFIC_FILE = ROOT / "profiles" / "ncu_traffic.json"
@@ -360,6 +361,7 @@ def run_gpu(args):
         return
 
     # ---- device-resident timing
+    barrier()   # the ranks built their weights at different speeds; start the first step together
     for i in range(args.warmup):
         step(i)
     barrier()
@@ -367,18 +369,65 @@ def run_gpu(args):
     # (status 401 / 402 / 403), say so in the line and measure the push form instead of
     # publishing numbers computed on poisoned activations.
     reduce_note = None
-    if world > 1:
+
+    def status_over_ranks():
         code = torch.tensor([float(native.device_status())], device=device)
-        dist.all_reduce(code, op=dist.ReduceOp.MAX)
-        if code.item() != 0.0:
-            reduce_note = f"owner form gave up during warm-up (device status {int(code.item())})"
-            collective.poll_status()
-            for ws in list(collective._workspaces.values()):
-                ws.reset()
-            owner = False
-            for i in range(args.warmup):
-                step(i)
+        if world > 1:
+            dist.all_reduce(code, op=dist.ReduceOp.MAX)
+        return int(code.item())
+
+    def fall_back(where, code):
+        nonlocal owner, reduce_note
+        reduce_note = f"owner form gave up during {where} (device status {code})"
+        collective.poll_status()
+        for ws in list(collective._workspaces.values()):
+            ws.reset()
+        owner = False
+        for i in range(args.warmup):
+            step(i)
+        barrier()
+
+    if world > 1:
+        code = status_over_ranks()
+        if code != 0:
+            fall_back("warm-up", code)
+
+    # The steps of the loop are captured once per (input, weight set) pair and replayed, as a
+    # serving engine does: with N ranks a step lasts little longer than the Python and ctypes
+    # calls that launch its kernels one by one, and a host thread that is descheduled for a
+    # moment would stall every rank through the reduce.
+    def capture_steps():
+        graphs = []
+        try:
+            side = torch.cuda.Stream(device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for j in range(STEP_VARIANTS):
+                    step(j)
+            torch.cuda.current_stream().wait_stream(side)
             barrier()
+            for j in range(STEP_VARIANTS):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    result = step(j)
+                graphs.append((graph, result))
+            barrier()
+        except RuntimeError:
+            graphs = []
+        ok = torch.tensor([1.0 if graphs else 0.0], device=device)
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)   # every rank takes the same route
+        return graphs if ok.item() != 0.0 else []
+
+    step_graphs = [] if args.no_step_graphs else capture_steps()
+
+    def run_step(i):
+        if step_graphs:
+            graph, result = step_graphs[i % STEP_VARIANTS]
+            graph.replay()
+            return result
+        return step(i)
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -389,7 +438,7 @@ def run_gpu(args):
     soak_until = time.perf_counter() + args.soak
     while args.soak > 0:
         for i in range(16):
-            step(soak_steps + i)
+            run_step(soak_steps + i)
         soak_steps += 16
         torch.cuda.synchronize()
         flag = torch.tensor([1.0 if time.perf_counter() < soak_until else 0.0], device=device)
@@ -397,14 +446,27 @@ def run_gpu(args):
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if flag.item() == 0.0:
             break
+    if world > 1 and owner:
+        code = status_over_ranks()
+        if code != 0:
+            fall_back("the soak", code)
+            step_graphs = [] if args.no_step_graphs else capture_steps()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     start.record()
     for i in range(args.steps):
-        out = step(i)
+        out = run_step(i)
+        marks[i].record()
     end.record()
     barrier()
     ms = start.elapsed_time(end)
+    ms_rank = ms
+    # longest single step of this rank (diagnostic: a stalled rank shows up here)
+    edges = [start] + marks
+    step_ms = [edges[i].elapsed_time(edges[i + 1]) for i in range(args.steps)]
+    worst_step = max(range(args.steps), key=lambda i: step_ms[i])
+    status_timed = status_over_ranks() if world > 1 else native.device_status()
     assert torch.isfinite(out[0].float()).all()
 
     # ---- dominant kernel (gate_up GEMM with the SwiGLU epilogue): every launch timed with its
@@ -489,12 +551,16 @@ def run_gpu(args):
                     s_in.wait_event(ev_free[b])
                 if even_split:
                     dev_in[b][rows_lo:rows_hi].copy_(host_in[b][rows_lo:rows_hi], non_blocking=True)
-                    dist.all_gather_into_tensor(dev_in[b], dev_in[b][rows_lo:rows_hi], group=group)
                 else:
                     dev_in[b].copy_(host_in[b], non_blocking=True)
                 ev_in[b].record(s_in)
             with torch.cuda.stream(s_run):
                 s_run.wait_event(ev_in[b])
+                if even_split:
+                    # On the compute stream, not beside it: the all-gather and the fused reduce
+                    # both wait for their peers on the device, and two such kernels of one GPU
+                    # in two streams can each hold the SMs the other one needs on another rank.
+                    dist.all_gather_into_tensor(dev_in[b], dev_in[b][rows_lo:rows_hi], group=group)
                 if graphs:
                     # the graph's output buffer is reused by its next replay: wait for the
                     # download that still reads it
@@ -529,15 +595,26 @@ def run_gpu(args):
     barrier()
     s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s2.record()
+    host_t0 = time.perf_counter()
     e2e_steps(args.steps)
+    e2e_host_ms = (time.perf_counter() - host_t0) * 1e3   # time to enqueue the steps
     e2.record()
     barrier()
     e2e_ms = s2.elapsed_time(e2)
     clocks = sampler.stop() if rank == 0 else None
 
     times = torch.tensor([ms, e2e_ms, k_ms], dtype=torch.float64, device=device)
+    ms_all = [ms_rank]
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        gathered = [torch.zeros(3, dtype=torch.float64, device=device) for _ in range(world)]
+        dist.all_gather(gathered, torch.tensor([ms_rank, step_ms[worst_step], float(worst_step)],
+                                               dtype=torch.float64, device=device))
+        ms_all = [float(t[0].item()) for t in gathered]
+        if rank == 0:
+            print("timed steps by rank (ms total, longest step ms, its index): " +
+                  ", ".join(f"{t[0].item():.3f}/{t[1].item():.3f}/{int(t[2].item())}"
+                            for t in gathered), file=sys.stderr)
     ms, e2e_ms, k_ms = times.tolist()
     status = native.device_status()
 
@@ -598,11 +675,14 @@ def run_gpu(args):
                        "tokens": m, "parallelism": f"tp{world}", "soak_steps": soak_steps,
                        "reduce": "owner form" if owner else ("push form" if world > 1 else "none"),
                        "reduce_note": reduce_note,
+                       "launch": ("CUDA graph replay, one graph per (input, weight set) pair"
+                                  if step_graphs else "kernels launched one by one"),
                        "step_outputs": outputs,
                        "l2": f"rotates {NUM_WEIGHT_SETS} weight sets "
                              f"({NUM_WEIGHT_SETS * sets[0].nbytes() * world / 1e6:.0f} MB > 126 MB L2)"},
             "e2e": {"value": m * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": m * HIDDEN * 2, "d2h_bytes_per_step": m * HIDDEN * 2,
+                    "host_enqueue_ms_per_step": e2e_host_ms / args.steps,
                     "note": ("bytes over all ranks; each rank moves the rows it owns and the "
                              "ranks all-gather the input over NVLink" if world > 1 else
                              "upload, kernels and download on three streams, double-buffered")
@@ -611,6 +691,8 @@ def run_gpu(args):
             "gpu_launches": 4 * args.steps,
             "roofline": roofline,
             "clocks": clocks, "device_status": status,
+            "device_status_after_timed_steps": status_timed,
+            "ms_per_step_by_rank": [t / args.steps for t in ms_all],
         }
         if parity is not None:
             line["parity"] = parity
@@ -1107,6 +1189,8 @@ def main():
     ap.add_argument("--no-tp-suite", action="store_true",
                     help="skip the MXFP6 MLP / MoE tensor-parallel timings")
     ap.add_argument("--no-library", action="store_true", help="skip the cuBLASLt FP8 peak")
+    ap.add_argument("--no-step-graphs", action="store_true",
+                    help="launch the kernels of the timed steps one by one instead of replaying graphs")
     ap.add_argument("--no-e2e-graphs", action="store_true",
                     help="end-to-end leg: launch the kernels one by one instead of replaying graphs")
     ap.add_argument("--no-owner", action="store_true",
