@@ -187,7 +187,8 @@ def tp_step(x, residual, residual_rows, gamma, w, group, owner):
     one GPU, return norm and residual for all rows."""
     from mach_b200.mlp import mlp_block, mlp_block_owner
     if owner or group is None:
-        codes, scales, res_rows, norm_rows = mlp_block_owner(x, residual_rows, gamma, EPS, w, group)
+        codes, scales, res_rows, norm_rows = mlp_block_owner(x, residual_rows, gamma, EPS, w, group,
+                                                             codes_in_workspace=True)
         return norm_rows, (codes, scales, res_rows)
     norm, res = mlp_block(x, residual, gamma, EPS, w, group)
     return norm, (res,)
@@ -454,6 +455,13 @@ def run_gpu(args):
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    if world > 1:
+        # A rank whose host thread leaves the barrier late would be waited for inside the first
+        # step's reduce of every other rank. This all-reduce is only ENQUEUED here: the device
+        # passes it once every rank has enqueued it, and each host follows it at once with the
+        # start event and the steps, so the timed region starts on all ranks together.
+        gate = torch.zeros(1, device=device)
+        dist.all_reduce(gate)
     start.record()
     for i in range(args.steps):
         out = run_step(i)
@@ -661,7 +669,8 @@ def run_gpu(args):
             ref = library.get("mxfp8_gate_up_4096x19456x2560", {})
             if "sustained" in ref:
                 roofline["vs_library_mxfp8_gate_up"] = achieved / ref["sustained"]
-        outputs = ("MXFP8 codes + scales replicated; BF16 norm and residual stream row-owned "
+        outputs = ("MXFP8 codes + scales replicated (read in the communication buffer, where "
+                   "the rows' owners store them); BF16 norm and residual stream row-owned "
                    "(1/N of the rows per rank)") if owner else \
                   "BF16 norm + residual (all rows)" if world > 1 else \
                   "BF16 norm + residual + MXFP8 codes + scales"
@@ -704,6 +713,9 @@ def run_gpu(args):
             line["cpu_baseline"] = cpu_baseline
         print(json.dumps(line))
     if world > 1:
+        graphs.clear()
+        step_graphs.clear()
+        torch.cuda.synchronize()
         collective.close_all()
         dist.destroy_process_group()
 
@@ -756,7 +768,8 @@ def run_tp_suite(group, world, rank, device, peaks):
         first, count = collective.owner_rows(m, group)
         rows = residual[first:first + count].contiguous()
         if owner:
-            fn = lambda i: mlp_block_owner(x, rows, gamma, EPS, sets[i % n_sets], group)  # noqa: E731
+            fn = lambda i: mlp_block_owner(x, rows, gamma, EPS, sets[i % n_sets], group,  # noqa: E731
+                                           codes_in_workspace=True)
         else:
             fn = lambda i: mlp_block(x, residual, gamma, EPS, sets[i % n_sets], group)  # noqa: E731
         us = timed(fn, n_sets, 10)

@@ -264,17 +264,24 @@ MACH_API int mach_allreduce_residual_rmsnorm_mxfp8(void* workspace, const void* 
  * gather_mx8 of native/owner_prefill/owner.cu:64-160 for any world <= 8 and any M): rank r owns
  * rows [first, first + count) given by mach_ar_owner_rows (contiguous blocks of ceil(M / world)).
  * Every owner pulls its rows of all ranks' partial sums over NVLink, reduces them in rank
- * order, adds ITS rows of the residual, normalises and quantises them; then every rank pulls
- * the other owners' codes and scales. Outputs: codes E4M3 [M, H] + swizzled E8M0 scales for ALL
+ * order, adds ITS rows of the residual, normalises and quantises them, and stores each row's
+ * codes and scales into every rank's communication buffer as it produces them (the stores run
+ * beside the pulls; one flag exchange closes the step). Outputs: codes E4M3 [M, H] + swizzled E8M0 scales for ALL
  * rows on every rank (what the next block-scaled GEMM consumes); residual_out_rows and
  * norm_out_rows (may be NULL) BF16 [count, H] for the OWNED rows only; residual_rows is BF16
  * [count, H], the owned rows of the residual stream. Same arithmetic and rounding points as
  * mach_allreduce_residual_rmsnorm_mxfp8, hence the same bytes.
  * partial_bf16 == NULL: the producing GEMM wrote its BF16 [M, H] output (leading dimension H)
  * to the address mach_ar_partial_ptr returns (inside this rank's communication buffer, fixed
- * for the life of the workspace), which saves one local copy. Launched cooperatively. */
+ * for the life of the workspace), which saves one local copy.
+ * codes / scales == the addresses mach_ar_codes_ptr returns (the all-rows code matrix and the
+ * swizzled scale buffer inside this rank's communication buffer, fixed for the life of the
+ * workspace): nothing is copied out, the next GEMM reads them where they are. They stay valid
+ * until the next reduce on the same workspace is launched; any other pair of pointers receives
+ * a copy. Launched cooperatively. */
 MACH_API int mach_ar_owner_rows(int world, int rank, int64_t m, int64_t* first, int64_t* count);
 MACH_API int mach_ar_partial_ptr(void* workspace, void** partial_bf16);
+MACH_API int mach_ar_codes_ptr(void* workspace, void** codes, void** scales);
 MACH_API int mach_allreduce_owner_rmsnorm_mxfp8(void* workspace, const void* partial_bf16,
                                                 const void* residual_rows_bf16,
                                                 const void* gamma_bf16, float eps,

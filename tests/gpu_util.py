@@ -81,9 +81,20 @@ class LocalRanks:
                            "ar_partial_ptr")
         return self.native.tensor_from_ptr(p.value, (m, self.hidden), torch.bfloat16, "cuda:0")
 
-    def run(self, partials, residuals, gamma, eps, m, algo=0, owner=False, weight_bias=1.0):
+    def codes_buffer(self, rank: int, m: int):
+        import ctypes
+        c, s = ctypes.c_void_p(), ctypes.c_void_p()
+        self.native._check(self.lib.mach_ar_codes_ptr(self.handles[rank], ctypes.byref(c),
+                                                      ctypes.byref(s)), "ar_codes_ptr")
+        return (self.native.tensor_from_ptr(c.value, (m, self.hidden), torch.uint8, "cuda:0"),
+                self.native.tensor_from_ptr(s.value, (self.native.sf_bytes(m, self.hidden),),
+                                            torch.uint8, "cuda:0"))
+
+    def run(self, partials, residuals, gamma, eps, m, algo=0, owner=False, weight_bias=1.0,
+            in_place=False):
         """partials / residuals: per-rank CUDA tensors (partials[r] may be None in the owner
-        form). Returns per-rank (norm, residual_out, codes, scales)."""
+        form). in_place (owner form): the codes and scales are the views of each rank's own
+        communication buffer. Returns per-rank (norm, residual_out, codes, scales)."""
         import ctypes
         native, world, h = self.native, self.world, self.hidden
         outs = []
@@ -93,10 +104,16 @@ class LocalRanks:
                 first, count = ctypes.c_int64(), ctypes.c_int64()
                 self.lib.mach_ar_owner_rows(world, r, m, ctypes.byref(first), ctypes.byref(count))
                 rows = count.value
+            if in_place:
+                codes, scales = self.codes_buffer(r, m)
+                codes.zero_()
+                scales.zero_()
+            else:
+                codes = torch.zeros((m, h), dtype=torch.uint8, device="cuda")
+                scales = torch.zeros(native.sf_bytes(m, h), dtype=torch.uint8, device="cuda")
             outs.append((torch.full((rows, h), 7.0, dtype=torch.bfloat16, device="cuda"),
                          torch.full((rows, h), 7.0, dtype=torch.bfloat16, device="cuda"),
-                         torch.zeros((m, h), dtype=torch.uint8, device="cuda"),
-                         torch.zeros(native.sf_bytes(m, h), dtype=torch.uint8, device="cuda")))
+                         codes, scales))
 
         def ptrs(tensors):
             return (ctypes.c_void_p * world)(*[None if t is None else t.data_ptr() for t in tensors])

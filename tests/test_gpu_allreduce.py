@@ -78,8 +78,10 @@ def _worker(rank, world, port, results):
                     dev_partial = None
                 else:
                     dev_partial = partials[rank].cuda()
+                # every other pair of cases reads the codes where their owners stored them
                 codes, scales, res_rows, norm_rows = collective.allreduce_owner_add_rmsnorm(
-                    dev_partial, rows, gamma.cuda(), eps, group, m)
+                    dev_partial, rows, gamma.cuda(), eps, group, m,
+                    codes_in_workspace=(it // 2) % 2 == 1)
                 torch.cuda.synchronize()
                 ref_norm, ref_res = ora.allreduce_rmsnorm(partials, residual, gamma, eps)
                 tag = f"owner h{h} m{m} rank{rank}"
@@ -169,7 +171,8 @@ def _worker(rank, world, port, results):
             first, count = collective.owner_rows(m, group)
             for rep in range(2):
                 codes, scales, res_rows, norm_rows = mlp_block_owner(
-                    x, residual[first:first + count].contiguous(), gamma, eps, weights, group)
+                    x, residual[first:first + count].contiguous(), gamma, eps, weights, group,
+                    codes_in_workspace=rep == 1)
             torch.cuda.synchronize()
             tag = f"owner block m{m} rank{rank}"
             if native.device_status() != 0:

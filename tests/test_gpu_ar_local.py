@@ -78,6 +78,7 @@ def test_owner_form_all_ranks_on_one_device(world, h):
             rpo = (m + world - 1) // world
             owned = [(min(r * rpo, m), max(0, min(rpo, m - min(r * rpo, m)))) for r in range(world)]
             in_buffer = it % 2 == 1   # alternate: partial tensor / written into the buffer
+            in_place = (it // 2) % 2 == 1   # codes and scales read where the owners stored them
             dev_partials = []
             for r in range(world):
                 if in_buffer:
@@ -86,7 +87,8 @@ def test_owner_form_all_ranks_on_one_device(world, h):
                 else:
                     dev_partials.append(partials[r].cuda())
             residual_rows = [residual[f:f + c].contiguous().cuda() for f, c in owned]
-            outs = group.run(dev_partials, residual_rows, gamma.cuda(), EPS, m, owner=True)
+            outs = group.run(dev_partials, residual_rows, gamma.cuda(), EPS, m, owner=True,
+                             in_place=in_place)
             assert native.device_status() == 0
             norm_full = torch.cat([o[0] for o in outs], 0)
             res_full = torch.cat([o[1] for o in outs], 0)

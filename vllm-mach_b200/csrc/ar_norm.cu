@@ -55,7 +55,8 @@ struct ArWorkspace {
   int64_t tokens_cap, hidden;
   size_t parity_bytes;          // bytes of one parity half of the push-form data area
   size_t owner_partial_off;     // owner form: BF16 partial sums [tokens_cap, hidden]
-  size_t owner_stage_off;       // owner form: codes [tokens_cap, hidden] then scales [tokens_cap, hidden/32]
+  size_t owner_stage_off;       // owner form: codes of ALL rows [tokens_cap, hidden] ...
+  size_t owner_scales_off;      // ... and their swizzled scales, written by the rows' owners
   long long wait_cycles;
 #ifdef MACH_EXPERIMENTS
   unsigned long long* trace;
@@ -84,7 +85,7 @@ struct ArParams {
   int prescattered;        // two-shot: the partial rows are already in the owners' slots
   int coarse;              // two-shot: one flag per (rank, phase) instead of one per CTA
   int owner;               // owner form
-  size_t parity_bytes, owner_partial_off, owner_stage_off;
+  size_t parity_bytes, owner_partial_off, owner_stage_off, owner_scales_off;
 #ifdef MACH_EXPERIMENTS
   unsigned long long* trace;  // phase time stamps of CTA 0: [epoch % 64][8] (globaltimer, ns)
 #endif
@@ -226,10 +227,13 @@ struct RowOut {
   __nv_bfloat16* res;      // residual_out row
   __nv_bfloat16* norm;     // norm row
   uint8_t* codes;          // E4M3 row
-  uint8_t* codes2;         // second copy of the codes (owner form: staging for the peers)
   uint8_t* scales;         // swizzled scale buffer (whole tensor) or null
-  uint8_t* scales2;        // logical scale row (owner form staging) or null
   int scale_row;           // row index inside the swizzled buffer
+  // owner form: the row's codes and scales also go to every other rank's buffer, at the same
+  // place of its all-rows code matrix and swizzled scale buffer
+  bool bcast;
+  size_t peer_codes_off;   // byte offset of the row's codes inside a rank's buffer
+  size_t peer_scales_off;  // byte offset of the swizzled scale buffer inside a rank's buffer
 };
 
 // residual add + RMSNorm (+ quant) of one row whose reduced BF16 sum is `a` (this thread's
@@ -299,11 +303,26 @@ __device__ __forceinline__ void norm_row(const ArParams& p, const __nv_bfloat16*
                    __fmul_rn(y[7], inv));
       if (poison) q = make_uint2(0x7F7F7F7Fu, 0x7F7F7F7Fu);
       *reinterpret_cast<uint2*>(out.codes + col) = q;
-      if (out.codes2) *reinterpret_cast<uint2*>(out.codes2 + col) = q;
+      if (out.bcast && !poison) {
+        for (int d = 1; d < p.world; ++d)
+          *reinterpret_cast<uint2*>(p.peers[(p.rank + d) % p.world] + out.peer_codes_off + col) = q;
+      }
       if ((threadIdx.x & 3) == 0) {
         const uint8_t sb = poison ? (uint8_t)0xFF : (uint8_t)(bits >> 23);
         if (out.scales) out.scales[sf_offset(out.scale_row, col >> 5, p.k_tiles)] = sb;
-        if (out.scales2) out.scales2[col >> 5] = sb;
+      }
+    }
+    if (out.bcast && !poison) {
+      // Four consecutive scale bytes of a row are one aligned word of the swizzled layout:
+      // lane 16j collects the bytes its 16 threads produced (lanes 16j, +4, +8, +12; threads
+      // past the row contribute 0, which lands in the layout's padding).
+      uint32_t w = have ? (bits >> 23) & 0xFFu : 0u;
+      w |= __shfl_down_sync(0xffffffffu, w, 4) << 8;
+      w |= __shfl_down_sync(0xffffffffu, w, 8) << 16;
+      if ((threadIdx.x & 15) == 0 && have) {
+        const size_t off = out.peer_scales_off + sf_offset(out.scale_row, col >> 5, p.k_tiles);
+        for (int d = 1; d < p.world; ++d)
+          *reinterpret_cast<uint32_t*>(p.peers[(p.rank + d) % p.world] + off) = w;
       }
     }
   }
@@ -314,10 +333,11 @@ __device__ __forceinline__ RowOut full_row_out(const ArParams& p, int row) {
   o.res = p.res_out ? p.res_out + (size_t)row * p.h : nullptr;
   o.norm = p.norm_out ? p.norm_out + (size_t)row * p.h : nullptr;
   o.codes = p.codes ? p.codes + (size_t)row * p.h : nullptr;
-  o.codes2 = nullptr;
   o.scales = p.scales;
-  o.scales2 = nullptr;
   o.scale_row = row;
+  o.bcast = false;
+  o.peer_codes_off = 0;
+  o.peer_scales_off = 0;
   return o;
 }
 
@@ -361,8 +381,10 @@ __device__ __forceinline__ void owner_body(const ArParams& p, uint8_t* mine, uin
   // With kPrefetch the loads of the CTA's NEXT row are issued before the current row is
   // reduced and normalised, so the NVLink round trip of one row hides behind the arithmetic
   // (and the block barriers) of another; rows of one CTA are otherwise strictly sequential.
-  uint8_t* stage_codes = mine + p.owner_stage_off;
-  uint8_t* stage_scales = stage_codes + (size_t)p.m * p.h;
+  // The caller's code and scale tensors may BE this rank's all-rows buffers (zero copy).
+  uint8_t* local_codes = mine + p.owner_stage_off;
+  uint8_t* local_scales = mine + p.owner_scales_off;
+  const bool in_place = p.codes == local_codes && p.scales == local_scales;
   auto issue = [&](int j, uint4 (&v)[kMaxWorld]) {
     const int row = first + j;
 #pragma unroll
@@ -408,10 +430,11 @@ __device__ __forceinline__ void owner_body(const ArParams& p, uint8_t* mine, uin
     o.res = p.res_out ? p.res_out + (size_t)j * p.h : nullptr;
     o.norm = p.norm_out ? p.norm_out + (size_t)j * p.h : nullptr;
     o.codes = p.codes + (size_t)row * p.h;
-    o.codes2 = stage_codes + (size_t)j * p.h;
     o.scales = p.scales;
-    o.scales2 = stage_scales + (size_t)j * groups;
     o.scale_row = row;
+    o.bcast = true;
+    o.peer_codes_off = p.owner_stage_off + (size_t)row * p.h;
+    o.peer_scales_off = p.owner_scales_off;
     norm_row(p, p.residual + (size_t)j * p.h, o, col, have, poison, a, warp_sums);
     if (kPrefetch) {
 #pragma unroll
@@ -428,84 +451,31 @@ __device__ __forceinline__ void owner_body(const ArParams& p, uint8_t* mine, uin
   }
   MACH_TRACE(p, target - 1, 5);
 
-  // ---- (2) the other owners' codes and scales. One flat index space over (owner, vector):
-  // a thread first issues up to eight peer loads (different owners, all in flight together),
-  // then stores them; a loop of dependent load -> store pairs would be bound by NVLink latency.
+  // ---- (2) the other owners' rows are in this rank's buffer now (their owners stored them
+  // there while they produced them, so the NVLink stores ran beside the pulls of phase 1).
+  // A caller that reads the buffer itself is done; otherwise they are copied to its tensors.
+  // After a failed wait nothing in the buffer can be trusted: every row this rank does not own
+  // is poisoned.
+  if (in_place && !poison) return;
   const int vpr = p.h >> 4;  // 16-byte vectors per row of codes
   const int tid = cta * blockDim.x + threadIdx.x;
   const int stride = ctas * blockDim.x;
-  {
-    const int seg = rpo * vpr;
-    const int total = (p.world - 1) * seg;
-    for (int base = tid; base < total; base += 8 * stride) {
-      uint4 v[8];
-      size_t dst[8];
-      bool valid[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int idx = base + u * stride;
-        valid[u] = false;
-        if (idx < total) {
-          const int d = idx / seg;
-          const int r = idx - d * seg;
-          const int o = (p.rank + 1 + d) % p.world;
-          const int ofirst = min(o * rpo, p.m);
-          const int ocount = min(rpo, p.m - ofirst);
-          if (r < ocount * vpr) {
-            valid[u] = true;
-            dst[u] = (size_t)ofirst * p.h + (size_t)r * 16;
-            v[u] = poison ? make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu)
-                          : ld_peer16(p.peers[o] + p.owner_stage_off + (size_t)r * 16);
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        if (valid[u]) *reinterpret_cast<uint4*>(p.codes + dst[u]) = v[u];
-    }
-  }
-  const size_t scale_base = p.owner_stage_off + (size_t)p.m * p.h;
-  if ((groups & 3) == 0) {
-    const int wpr = groups >> 2;  // 4-byte words per row of scales
-    const int seg = rpo * wpr;
-    const int total = (p.world - 1) * seg;
-    for (int base = tid; base < total; base += 4 * stride) {
-      uint32_t v[4];
-      size_t dst[4];
-      bool valid[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int idx = base + u * stride;
-        valid[u] = false;
-        if (idx < total) {
-          const int d = idx / seg;
-          const int r = idx - d * seg;
-          const int o = (p.rank + 1 + d) % p.world;
-          const int ofirst = min(o * rpo, p.m);
-          const int ocount = min(rpo, p.m - ofirst);
-          if (r < ocount * wpr) {
-            const int j = r / wpr, w = r - j * wpr;
-            valid[u] = true;
-            dst[u] = sf_offset(ofirst + j, w * 4, p.k_tiles);
-            v[u] = poison ? 0xFFFFFFFFu : ld_peer4(p.peers[o] + scale_base + (size_t)r * 4);
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (valid[u]) *reinterpret_cast<uint32_t*>(p.scales + dst[u]) = v[u];
-    }
-  } else {
-    for (int d = 1; d < p.world; ++d) {
-      const int o = (p.rank + d) % p.world;
-      const int ofirst = min(o * rpo, p.m);
-      const int ocount = min(rpo, p.m - ofirst);
-      const int bytes = ocount * groups;
-      for (int idx = tid; idx < bytes; idx += stride) {
-        const int j = idx / groups, g = idx - j * groups;
-        p.scales[sf_offset(ofirst + j, g, p.k_tiles)] =
-            poison ? (uint8_t)0xFF : (uint8_t)ld_peer1(p.peers[o] + scale_base + idx);
-      }
+  const uint4 bad = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+  for (int d = 1; d < p.world; ++d) {
+    const int o = (p.rank + d) % p.world;
+    const int ofirst = min(o * rpo, p.m);
+    const int ocount = min(rpo, p.m - ofirst);
+    const int total = ocount * vpr;
+    const uint4* src = reinterpret_cast<const uint4*>(local_codes + (size_t)ofirst * p.h);
+    uint4* dst = reinterpret_cast<uint4*>(p.codes + (size_t)ofirst * p.h);
+    for (int idx = tid; idx < total; idx += stride)
+      dst[idx] = poison ? bad : ld_cg(src + idx);
+    // scale bytes of one row: groups consecutive bytes at four-byte granularity
+    const int bytes = ocount * groups;
+    for (int idx = tid; idx < bytes; idx += stride) {
+      const int j = idx / groups, g = idx - j * groups;
+      const size_t off = sf_offset(ofirst + j, g, p.k_tiles);
+      p.scales[off] = poison ? (uint8_t)0xFF : __ldcg(local_scales + off);
     }
   }
 }
@@ -731,8 +701,14 @@ size_t parity_bytes_for(int world, int64_t tokens_cap, int64_t hidden) {
 size_t owner_partial_bytes(int64_t tokens_cap, int64_t hidden) {
   return ((size_t)tokens_cap * hidden * 2 + 255) & ~(size_t)255;
 }
+// Owner form: codes of all rows [tokens_cap, hidden], then their swizzled scales (one 512-byte
+// atom per 128 rows x 128 columns).
+size_t owner_codes_bytes(int64_t tokens_cap, int64_t hidden) {
+  return ((size_t)tokens_cap * hidden + 255) & ~(size_t)255;
+}
 size_t owner_stage_bytes(int64_t tokens_cap, int64_t hidden) {
-  return ((size_t)tokens_cap * (hidden + hidden / 32) + 255) & ~(size_t)255;
+  const size_t atoms = (size_t)((tokens_cap + 127) / 128) * (size_t)((hidden + 127) / 128);
+  return owner_codes_bytes(tokens_cap, hidden) + atoms * 512;
 }
 
 constexpr long long kDefaultWaitCycles = kWaitCycles;
@@ -792,6 +768,7 @@ int fill_params(ArWorkspace* ws, const void* partial, const void* residual, cons
   p.parity_bytes = ws->parity_bytes;
   p.owner_partial_off = ws->owner_partial_off;
   p.owner_stage_off = ws->owner_stage_off;
+  p.owner_scales_off = ws->owner_scales_off;
   p.owner = owner ? 1 : 0;
   if (owner) {
     *out = p;
@@ -993,6 +970,7 @@ extern "C" int mach_ar_create(int world, int rank, int64_t tokens_cap, int64_t h
   ws->parity_bytes = parity_bytes_for(world, tokens_cap, hidden);
   ws->owner_partial_off = kHeaderBytes + 2 * ws->parity_bytes;
   ws->owner_stage_off = ws->owner_partial_off + owner_partial_bytes(tokens_cap, hidden);
+  ws->owner_scales_off = ws->owner_stage_off + owner_codes_bytes(tokens_cap, hidden);
   ws->wait_cycles = kDefaultWaitCycles;
   for (int i = 0; i < world; ++i) {
     if (!buffers[i]) {
@@ -1047,6 +1025,14 @@ extern "C" int mach_ar_partial_ptr(void* workspace, void** partial_bf16) {
   ArWorkspace* ws = reinterpret_cast<ArWorkspace*>(workspace);
   if (!ws || !partial_bf16) return fail(MACH_ERR_INVALID, "ar_partial_ptr: null pointer");
   *partial_bf16 = ws->peers[ws->rank] + ws->owner_partial_off;
+  return MACH_OK;
+}
+
+extern "C" int mach_ar_codes_ptr(void* workspace, void** codes, void** scales) {
+  ArWorkspace* ws = reinterpret_cast<ArWorkspace*>(workspace);
+  if (!ws || !codes || !scales) return fail(MACH_ERR_INVALID, "ar_codes_ptr: null pointer");
+  *codes = ws->peers[ws->rank] + ws->owner_stage_off;
+  *scales = ws->peers[ws->rank] + ws->owner_scales_off;
   return MACH_OK;
 }
 

@@ -101,6 +101,21 @@ class ArWorkspace:
         return native.tensor_from_ptr(self._partial_ptr, (m, self.hidden), torch.bfloat16,
                                       self.device)
 
+    def codes_buffer(self, m: int):
+        """(E4M3 [m, hidden], swizzled E8M0 scales) INSIDE this rank's communication buffer:
+        where the owners of the rows store them. Passing them as the outputs of the owner-form
+        reduce skips the copy into caller tensors; they are overwritten by the next reduce on
+        this workspace."""
+        if m > self.tokens_cap:
+            raise ValueError("more tokens than the workspace holds")
+        codes, scales = native._P(), native._P()
+        native._check(native.lib().mach_ar_codes_ptr(self.handle, ctypes.byref(codes),
+                                                     ctypes.byref(scales)), "ar_codes_ptr")
+        return (native.tensor_from_ptr(codes.value, (m, self.hidden), torch.float8_e4m3fn,
+                                       self.device),
+                native.tensor_from_ptr(scales.value, (native.sf_bytes(m, self.hidden),),
+                                       torch.uint8, self.device))
+
     def set_wait_limit_us(self, microseconds: int) -> None:
         native._check(native.lib().mach_ar_set_wait_limit_us(self.handle, int(microseconds)),
                       "ar_set_wait_limit_us")
@@ -341,9 +356,11 @@ def owner_partial_buffer(group, hidden: int, m: int, device) -> torch.Tensor | N
 
 def allreduce_owner_add_rmsnorm(partial, residual_rows, gamma, eps: float, group, m: int,
                                 weight_bias: float = 1.0, want_norm: bool = True,
-                                checked: bool = False):
+                                checked: bool = False, codes_in_workspace: bool = False):
     """Owner form. residual_rows: BF16 [count, H], this rank's rows (see `owner_rows`).
     partial: BF16 [m, H], or None when the GEMM wrote into `owner_partial_buffer`.
+    codes_in_workspace: return the codes and scales as views of this rank's communication
+    buffer (no copy; valid until the next reduce of this group and hidden size is launched).
     Returns (codes [m, H], scales, residual_out_rows [count, H], norm_rows [count, H] | None)."""
     native._require(residual_rows, torch.bfloat16, "residual_rows")
     native._require(gamma, torch.bfloat16, "gamma")
@@ -364,13 +381,16 @@ def allreduce_owner_add_rmsnorm(partial, residual_rows, gamma, eps: float, group
             partial, residual_rows, gamma, eps, weight_bias, want_norm=want_norm,
             want_quant=True, rounded_sum=True)
         return codes, scales, res, norm
-    codes = torch.empty((m, h), dtype=torch.float8_e4m3fn, device=dev)
-    scales = torch.empty((native.sf_bytes(m, h),), dtype=torch.uint8, device=dev)
     res = torch.empty_like(residual_rows)
     norm = torch.empty_like(residual_rows) if want_norm else None
+    ws = workspace_for(group, h, m, dev) if m else None
+    if codes_in_workspace and ws is not None and not ws.failed:
+        codes, scales = ws.codes_buffer(m)
+    else:
+        codes = torch.empty((m, h), dtype=torch.float8_e4m3fn, device=dev)
+        scales = torch.empty((native.sf_bytes(m, h),), dtype=torch.uint8, device=dev)
     if m == 0:
         return codes, scales, res, norm
-    ws = workspace_for(group, h, m, dev)
     if ws is None or ws.failed:
         if partial is None:
             raise RuntimeError("the fused all-reduce is unavailable and the partial sums were "

@@ -85,7 +85,7 @@ def mlp_block(x, residual, norm_weight, eps: float, w: MxMlpWeights, group=None)
 
 
 def mlp_block_owner(x, residual_rows, norm_weight, eps: float, w: MxMlpWeights, group=None,
-                    want_norm: bool = True):
+                    want_norm: bool = True, codes_in_workspace: bool = False):
     """MLP + deferred reduce with row ownership between norms (native/owner_prefill/owner.cu:
     64-160): the residual stream is row-owned (`collective.owner_rows`), the down projection
     writes its partial sums straight into this rank's communication buffer, every owner reduces,
@@ -107,4 +107,5 @@ def mlp_block_owner(x, residual_rows, norm_weight, eps: float, w: MxMlpWeights, 
                else mlp_forward(x, w, out=target))
     return collective.allreduce_owner_add_rmsnorm(None if target is not None else partial,
                                                   residual_rows, norm_weight, eps, group, m,
-                                                  want_norm=want_norm)
+                                                  want_norm=want_norm,
+                                                  codes_in_workspace=codes_in_workspace)

@@ -56,6 +56,7 @@ _SIGNATURES = {
     "mach_ar_reset": (_INT, [_P, _P]),
     "mach_ar_owner_rows": (_INT, [_INT, _INT, _I64, ctypes.POINTER(_I64), ctypes.POINTER(_I64)]),
     "mach_ar_partial_ptr": (_INT, [_P, ctypes.POINTER(_P)]),
+    "mach_ar_codes_ptr": (_INT, [_P, ctypes.POINTER(_P), ctypes.POINTER(_P)]),
     "mach_allreduce_owner_rmsnorm_mxfp8": (_INT, [_P, _P, _P, _P, _F, _F, _P, _P, _P, _P, _I64,
                                                   _I64, _P]),
     "mach_allreduce_local_ranks": (_INT, [_INT, ctypes.POINTER(_P), ctypes.POINTER(_P),
