@@ -44,6 +44,14 @@ SOAK_SECONDS = 1.0
 STEP_VARIANTS = 4         # step i uses input i % 4 and weight set i % NUM_WEIGHT_SETS
 KERNEL_TIMING_LAUNCHES = 200     # launches of the dominant kernel timed one by one
 OWNER_MIN_BYTES = 1 << 20        # tensor-parallel payloads above this take the owner form
+
+
+def owner_min_bytes(world: int) -> int:
+    """Payload from which the owner form is faster than the push form. Measured on B200s
+    (fused reduce alone, hidden 2560, microseconds push / owner): two GPUs 10.9 / 14.8 at 64
+    tokens and 15.9 / 15.7 at 256; four GPUs 15.7 / 15.8 and 18.6 / 16.9; eight GPUs 19.0 / 16.9
+    and 21.4 / 18.3."""
+    return OWNER_MIN_BYTES if world <= 2 else OWNER_MIN_BYTES // 4
 TRAFFIC_FILE = ROOT / "profiles" / "ncu_traffic.json"
 
 
@@ -211,7 +219,7 @@ def tp_parity(group, world, rank, device, tokens):
     gamma = (0.1 * torch.randn(HIDDEN, generator=g)).to(torch.bfloat16).to(device)
     w, (c_gu, l_gu, c_d, l_d) = make_weights(device, world, rank, 1000, logical=True)
     partial = mlp_forward(x, w)
-    owner = tokens * HIDDEN * 2 > OWNER_MIN_BYTES
+    owner = tokens * HIDDEN * 2 > owner_min_bytes(world)
     first, count = collective.owner_rows(tokens, group)
     if owner:
         norm_rows, (codes, scales, res_rows) = tp_step(
@@ -338,7 +346,7 @@ def run_gpu(args):
     peaks = measured_peaks()
     m = args.tokens
     _, inter_local = shard_blocks(INTER, world, rank)
-    owner = world > 1 and not args.no_owner and m * HIDDEN * 2 > OWNER_MIN_BYTES
+    owner = world > 1 and not args.no_owner and m * HIDDEN * 2 > owner_min_bytes(world)
 
     sets = [make_weights(device, world, rank, 1000 + i) for i in range(NUM_WEIGHT_SETS)]
     g = torch.Generator(device=device).manual_seed(7)
@@ -764,7 +772,7 @@ def run_tp_suite(group, world, rank, device, peaks):
     for m in (1, 32, 512, 4096):
         x = torch.randn(m, hid, generator=g, device=device).to(torch.bfloat16)
         residual = torch.randn(m, hid, generator=g, device=device).to(torch.bfloat16)
-        owner = world > 1 and m * hid * 2 > OWNER_MIN_BYTES
+        owner = world > 1 and m * hid * 2 > owner_min_bytes(world)
         first, count = collective.owner_rows(m, group)
         rows = residual[first:first + count].contiguous()
         if owner:
@@ -813,7 +821,7 @@ def run_tp_suite(group, world, rank, device, peaks):
         _, ids = moe_mod.router_topk(logits, top_k)
         local_ids = ids[(ids // per) == rank] if world > 1 else ids
         distinct = int(torch.unique(local_ids).numel())
-        owner = world > 1 and m * hid * 2 > OWNER_MIN_BYTES
+        owner = world > 1 and m * hid * 2 > owner_min_bytes(world)
         first, count = collective.owner_rows(m, group)
         rows = residual[first:first + count].contiguous()
 
