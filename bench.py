@@ -406,7 +406,8 @@ def run_gpu(args):
     # calls that launch its kernels one by one, and a host thread that is descheduled for a
     # moment would stall every rank through the reduce.
     def capture_steps():
-        graphs = []
+        """([single-step graphs], chain graph of STEP_VARIANTS consecutive steps) or ([], None)."""
+        graphs, chain = [], None
         try:
             side = torch.cuda.Stream(device)
             side.wait_stream(torch.cuda.current_stream())
@@ -420,22 +421,44 @@ def run_gpu(args):
                 with torch.cuda.graph(graph):
                     result = step(j)
                 graphs.append((graph, result))
+            # Consecutive blocks of one graph keep the programmatic-dependent-launch chain across
+            # the block boundary, as the layers of a captured forward pass do.
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for j in range(STEP_VARIANTS):
+                    result = step(j)
+            chain = (graph, result)
             barrier()
         except RuntimeError:
-            graphs = []
+            graphs, chain = [], None
         ok = torch.tensor([1.0 if graphs else 0.0], device=device)
         if world > 1:
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)   # every rank takes the same route
-        return graphs if ok.item() != 0.0 else []
+        return (graphs, chain) if ok.item() != 0.0 else ([], None)
 
-    step_graphs = [] if args.no_step_graphs else capture_steps()
+    step_graphs, step_chain = ([], None) if args.no_step_graphs else capture_steps()
 
-    def run_step(i):
-        if step_graphs:
-            graph, result = step_graphs[i % STEP_VARIANTS]
-            graph.replay()
-            return result
-        return step(i)
+    def run_steps(first, count, marks=None, marked=None):
+        """Steps first .. first + count - 1 (first a multiple of STEP_VARIANTS): whole chains of
+        STEP_VARIANTS steps, then single steps. Records marks[i] after step i where it can (after
+        every step, or at the end of a chain). Returns the last step's result."""
+        result, i = None, first
+        while i < first + count:
+            if step_chain is not None and i % STEP_VARIANTS == 0 and i + STEP_VARIANTS <= first + count:
+                step_chain[0].replay()
+                result = step_chain[1]
+                i += STEP_VARIANTS
+            elif step_graphs:
+                graph, result = step_graphs[i % STEP_VARIANTS]
+                graph.replay()
+                i += 1
+            else:
+                result = step(i)
+                i += 1
+            if marks is not None:
+                marks[i - first - 1].record()
+                marked.append(i - first - 1)
+        return result
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -446,8 +469,7 @@ def run_gpu(args):
     soak_steps = 0
     soak_until = time.perf_counter() + args.soak
     while args.soak > 0:
-        for i in range(16):
-            run_step(soak_steps + i)
+        run_steps(soak_steps, 16)
         soak_steps += 16
         torch.cuda.synchronize()
         flag = torch.tensor([1.0 if time.perf_counter() < soak_until else 0.0], device=device)
@@ -459,7 +481,7 @@ def run_gpu(args):
         code = status_over_ranks()
         if code != 0:
             fall_back("the soak", code)
-            step_graphs = [] if args.no_step_graphs else capture_steps()
+            step_graphs, step_chain = ([], None) if args.no_step_graphs else capture_steps()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -471,16 +493,20 @@ def run_gpu(args):
         gate = torch.zeros(1, device=device)
         dist.all_reduce(gate)
     start.record()
-    for i in range(args.steps):
-        out = run_step(i)
-        marks[i].record()
+    marked = []
+    out = run_steps(0, args.steps, marks, marked)
     end.record()
     barrier()
     ms = start.elapsed_time(end)
     ms_rank = ms
-    # longest single step of this rank (diagnostic: a stalled rank shows up here)
-    edges = [start] + marks
-    step_ms = [edges[i].elapsed_time(edges[i + 1]) for i in range(args.steps)]
+    # longest stretch between two recorded marks, per step (diagnostic: a stalled rank shows up
+    # here); marks inside a chain of steps are not recorded
+    step_ms, last, last_i = [0.0] * args.steps, start, -1
+    for i in marked:
+        span = last.elapsed_time(marks[i]) / (i - last_i)
+        for j in range(last_i + 1, i + 1):
+            step_ms[j] = span
+        last, last_i = marks[i], i
     worst_step = max(range(args.steps), key=lambda i: step_ms[i])
     status_timed = status_over_ranks() if world > 1 else native.device_status()
     assert torch.isfinite(out[0].float()).all()
@@ -692,8 +718,11 @@ def run_gpu(args):
                        "tokens": m, "parallelism": f"tp{world}", "soak_steps": soak_steps,
                        "reduce": "owner form" if owner else ("push form" if world > 1 else "none"),
                        "reduce_note": reduce_note,
-                       "launch": ("CUDA graph replay, one graph per (input, weight set) pair"
-                                  if step_graphs else "kernels launched one by one"),
+                       "launch": (f"CUDA graph replay, {STEP_VARIANTS} consecutive steps per graph "
+                                  "(single-step graphs for the remainder)"
+                                  if step_chain is not None else
+                                  "CUDA graph replay, one graph per step" if step_graphs
+                                  else "kernels launched one by one"),
                        "step_outputs": outputs,
                        "l2": f"rotates {NUM_WEIGHT_SETS} weight sets "
                              f"({NUM_WEIGHT_SETS * sets[0].nbytes() * world / 1e6:.0f} MB > 126 MB L2)"},
@@ -723,6 +752,7 @@ def run_gpu(args):
     if world > 1:
         graphs.clear()
         step_graphs.clear()
+        step_chain = None
         torch.cuda.synchronize()
         collective.close_all()
         dist.destroy_process_group()
