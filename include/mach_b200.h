@@ -58,7 +58,12 @@ MACH_API int mach_abi_version(void);
 /* Text of the last error on the calling thread ("" if none). Host memory, never freed. */
 MACH_API const char* mach_last_error(void);
 /* Reads (synchronously) the device status word: 0 healthy, else the code of the first
- * device-side wait that gave up. Clears it when `clear` is non-zero. */
+ * device-side wait that gave up. Clears it when `clear` is non-zero. The hundreds digit names
+ * the kernel (1 feature-major MX GEMM, 2 block-FP8 tile GEMM, 3 single-CTA persistent MX GEMM,
+ * 4 fused all-reduce: 401 partial-sum flag, 402 result flag, 403 failed workspace, 5 grouped
+ * MoE GEMM, 6 CTA-pair MX GEMM, 7 persistent block-FP8 GEMM, 8 one-token-tile MX GEMM); the
+ * units digit the barrier (1 free stage, 2 filled stage, 3 finished accumulator, 4 drained
+ * accumulator). */
 MACH_API int mach_device_status(int* status_out, int clear);
 
 /* Bytes of a swizzled E8M0 scale buffer for `rows` x K. */

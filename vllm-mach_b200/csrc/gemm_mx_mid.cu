@@ -44,7 +44,7 @@ constexpr int kThreads = (2 + kEpiWarps) * 32;
 constexpr int kMaxStages = 8;
 constexpr int kSfCols = 4 + 4 * kMaxBAtoms;      // TMEM columns of the scale factors
 
-enum { kWaitEmpty = 701, kWaitFull = 702, kWaitAccum = 703 };
+enum { kWaitEmpty = 801, kWaitFull = 802, kWaitAccum = 803 };
 
 struct MidParams {
   const uint8_t* sf_a;
