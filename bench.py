@@ -407,7 +407,9 @@ def run_gpu(args):
     # moment would stall every rank through the reduce.
     def capture_steps():
         """([single-step graphs], chain graph of STEP_VARIANTS consecutive steps) or ([], None)."""
-        graphs, chain = [], None
+        graphs, chain, fine = [], None, True
+        # No collective call sits inside a try block: a rank whose capture fails still takes
+        # part in every barrier, and the vote below puts all ranks on the same route.
         try:
             side = torch.cuda.Stream(device)
             side.wait_stream(torch.cuda.current_stream())
@@ -415,22 +417,26 @@ def run_gpu(args):
                 for j in range(STEP_VARIANTS):
                     step(j)
             torch.cuda.current_stream().wait_stream(side)
-            barrier()
-            for j in range(STEP_VARIANTS):
+        except RuntimeError:
+            fine = False
+        barrier()
+        if fine:
+            try:
+                for j in range(STEP_VARIANTS):
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        result = step(j)
+                    graphs.append((graph, result))
+                # Consecutive blocks of one graph keep the programmatic-dependent-launch chain
+                # across the block boundary, as the layers of a captured forward pass do.
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph):
-                    result = step(j)
-                graphs.append((graph, result))
-            # Consecutive blocks of one graph keep the programmatic-dependent-launch chain across
-            # the block boundary, as the layers of a captured forward pass do.
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                for j in range(STEP_VARIANTS):
-                    result = step(j)
-            chain = (graph, result)
-            barrier()
-        except RuntimeError:
-            graphs, chain = [], None
+                    for j in range(STEP_VARIANTS):
+                        result = step(j)
+                chain = (graph, result)
+            except RuntimeError:
+                graphs, chain = [], None
+        barrier()
         ok = torch.tensor([1.0 if graphs else 0.0], device=device)
         if world > 1:
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)   # every rank takes the same route
@@ -558,6 +564,7 @@ def run_gpu(args):
     # than the Python and ctypes calls that launch them one by one.
     graphs = {}
     if not args.no_e2e_graphs:
+        fine = True
         try:
             side = torch.cuda.Stream(device)
             side.wait_stream(main)
@@ -566,17 +573,21 @@ def run_gpu(args):
                     for w in range(NUM_WEIGHT_SETS):
                         tp_step(dev_in[b], residual, residual_rows, gamma, sets[w], group, owner)
             main.wait_stream(side)
-            barrier()
-            for b in range(2):
-                for w in range(NUM_WEIGHT_SETS):
-                    graph = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(graph):
-                        result = tp_step(dev_in[b], residual, residual_rows, gamma, sets[w], group,
-                                         owner)
-                    graphs[(b, w)] = (graph, result)
-            barrier()
         except RuntimeError:
-            graphs = {}
+            fine = False
+        barrier()
+        if fine:
+            try:
+                for b in range(2):
+                    for w in range(NUM_WEIGHT_SETS):
+                        graph = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(graph):
+                            result = tp_step(dev_in[b], residual, residual_rows, gamma, sets[w],
+                                             group, owner)
+                        graphs[(b, w)] = (graph, result)
+            except RuntimeError:
+                graphs = {}
+        barrier()
     flag = torch.tensor([1.0 if graphs else 0.0], device=device)
     if world > 1:
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)   # every rank takes the same route
