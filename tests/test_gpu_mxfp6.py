@@ -39,7 +39,10 @@ def test_fp6_decode_through_identity_activations(nat, fmt):
 
 @pytest.mark.parametrize("fmt", ["e2m3", "e3m2"])
 @pytest.mark.parametrize("m,n,k", [(1, 256, 128), (32, 5120, 2176), (64, 2176, 5120), (512, 4352, 5120),
-                                   (300, 640, 384)])
+                                   (300, 640, 384),
+                                   # one token tile (49..128 tokens, wide matrix), and a narrow
+                                   # matrix at 256 tokens (feature-major, receive slots in the ring)
+                                   (100, 9728, 256), (128, 19456, 128), (256, 640, 384)])
 def test_w6a8_gemm(nat, fmt, m, n, k):
     x = randn_bf16(m, k, 5000 + m)
     packed, scales, deq = mxfp6_weight(n, k, 5001 + m, fmt)
@@ -53,9 +56,10 @@ def test_w6a8_gemm(nat, fmt, m, n, k):
     assert rel_fro(out, ref) <= 1e-2
 
 
-@pytest.mark.parametrize("m", [16, 200, 1024])
-def test_w6a8_fused_swiglu(nat, m):
-    inter, k, fmt = 1088, 640, "e2m3"
+@pytest.mark.parametrize("m,inter,k", [(16, 1088, 640), (200, 1088, 640), (1024, 1088, 640),
+                                       (100, 4864, 256)])   # the last: one-token-tile kernel
+def test_w6a8_fused_swiglu(nat, m, inter, k):
+    fmt = "e2m3"
     x = randn_bf16(m, k, 6000 + m)
     packed, scales, _ = mxfp6_weight(2 * inter, k, 6001 + m, fmt, sigma=0.05)
     a, sa = nat.quantize_mxfp8(x.cuda())
