@@ -9,7 +9,9 @@ copied into the repository: the cut goes to the git-ignored oracle/_ref/), and c
 with oracle/ar_ref_harness.cpp by g++ into a shared library that tests/test_oracle_cpu.py uses
 to pin oracle.mx_oracle.allreduce_rmsnorm and the MXFP8 activation rule.
 
-    python oracle/build_ref.py [reference root]      (default /root/reference)
+    python oracle/build_ref.py [reference root]
+                  (default: $MACH_REFERENCE_ROOT, else the `reference` checkout that lies
+                   beside this repository's folder)
 
 Returns silently without building when the reference checkout is absent (the GPU box): the
 prebuilt library travels with the repository snapshot.
@@ -21,7 +23,10 @@ import subprocess
 import sys
 from pathlib import Path
 
+import os
+
 HERE = Path(__file__).resolve().parent
+DEFAULT_REFERENCE = os.environ.get("MACH_REFERENCE_ROOT") or str(HERE.parent.parent / "reference")
 OUT = HERE / "_ref"
 LIB = OUT / "libar_ref.so"
 HEADER = "native/ar_norm/trtllm_allreduce_fusion_mxfp8.cuh"
@@ -62,7 +67,7 @@ def extract(text: str) -> str:
     return "\n".join(parts)
 
 
-def build(reference_root: str = "/root/reference", force: bool = False) -> Path | None:
+def build(reference_root: str = DEFAULT_REFERENCE, force: bool = False) -> Path | None:
     header = Path(reference_root) / HEADER
     if not header.exists():
         return LIB if LIB.exists() else None
