@@ -164,7 +164,7 @@ def test_large_batch_kernels_agree_bit_for_bit(nat, pair, m, n, k):
     assert bytes_equal(out, other)
 
 
-# One token tile (49..128 tokens) and a weight matrix with at least one 64-row group per SM:
+# One token tile (33..128 tokens) and a weight matrix with at least one 64-row group per SM:
 # balanced variable-width tiles. 9728 rows: 1-2 groups per CTA; 19456: 2-3; 66304: 7 (two MMAs,
 # 256 + 192 columns); 85248: two rounds of CTAs; 9744: a partial last group.
 @pytest.mark.parametrize("m,n,k", [(65, 9728, 384), (128, 19456, 256), (100, 66304, 128),
@@ -184,7 +184,8 @@ def test_one_token_tile_kernel_matches_dequant_matmul(nat, m, n, k):
     assert bytes_equal(out, other), mismatch_report(out, other)
 
 
-@pytest.mark.parametrize("m,inter,k", [(49, 4864, 256), (128, 9728, 2560), (96, 33152, 128)])
+@pytest.mark.parametrize("m,inter,k", [(33, 4864, 256), (49, 4864, 256), (128, 9728, 2560),
+                                       (96, 33152, 128)])
 def test_one_token_tile_swiglu_bit_exact(nat, m, inter, k):
     x = randn_bf16(m, k, 5000 + m)
     w_codes, w_scales, _ = mxfp8_weight(2 * inter, k, 5001 + m, sigma=0.05)

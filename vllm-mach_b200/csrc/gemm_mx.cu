@@ -643,7 +643,8 @@ int run_mx_gemm(const void* a_codes, const void* a_sf, const void* w, const void
   // Which orientation. Feature-major (weights on the 128-row side, cluster split-K) wins while
   // the batch is a small MMA-N; measured on B200 (graph replay, us):
   //   19456 x 2560 interleaved gate_up + SwiGLU   M = 32: 17.2 feature-major / 20.3 one token tile
-  //                                               M = 48: 20.3 / 19.1      M = 64: 22.7 / 17.5
+  //                                               M = 40: 20.3 / 20.0      M = 48: 20.3 / 19.1
+  //                                               M = 64: 22.7 / 17.5
   //   19456 x 2560 plain rows, BF16 out           M = 32: 15.0 / 15.6      M = 48: 17.3 / 15.3
   //                                               M = 64: 22.9 / 13.9
   //   2560 x 9728 (narrow: too few tiles for the token-major kernels)
@@ -652,8 +653,8 @@ int run_mx_gemm(const void* a_codes, const void* a_sf, const void* w, const void
   const bool mid_layout = interleaved || !swiglu;   // layouts the one-token-tile kernel takes
   const bool mid_shape = g_tune.mid != 0 && !scatter && mid_layout && mx_gemm_mid_fits(128, w_rows);
   const int64_t wide_max = g_tune.wide_max_m > 0 ? g_tune.wide_max_m
-                           : (swiglu && interleaved) ? 48
-                           : mid_shape ? 32 : 64;
+                           : mid_shape ? 32
+                           : (swiglu && interleaved) ? 48 : 64;
   const bool swap =
       m <= g_tune.swap_max_m && (m <= wide_max || (narrow && m <= g_tune.narrow_max_m));
   const bool token_major_pair =
